@@ -1,0 +1,214 @@
+/*
+ * b200pa.h — C ABI of the B200-native PagedAttention decode path.
+ *
+ * One shared library (libb200pa.so) exports the functions declared here.  They
+ * are the drop-in boundary for four operators of the reference project (vLLM):
+ *
+ *   torch.ops._C.paged_attention_v1            csrc/torch_bindings.cpp:52-63
+ *   torch.ops._C.paged_attention_v2            csrc/torch_bindings.cpp:65-77
+ *   torch.ops._C_cache_ops.reshape_and_cache   csrc/torch_bindings.cpp:687-694
+ *   torch.ops._C_cache_ops.reshape_and_cache_flash          ... :696-705
+ *   torch.ops._C_cache_ops.convert_fp8         csrc/torch_bindings.cpp:716-719
+ *
+ * Conventions
+ *   - Plain C: raw device pointers, sizes and element strides; no framework
+ *     types.  `stream` is a cudaStream_t passed as void* (NULL = legacy default
+ *     stream).  The current CUDA device must be the one that owns the pointers.
+ *   - Every function returns 0 on success or a negative B200PA_E* code; it never
+ *     throws and never aborts.  b200pa_last_error() returns a thread-local,
+ *     human-readable message for the last non-zero return on this thread.
+ *   - Like the reference ops, the launchers do not synchronise, do not allocate
+ *     device memory and do not read device data on the host, so they may be
+ *     recorded into a CUDA graph.
+ *   - No bounds checks on block-table or slot indices (same contract as the
+ *     reference kernels, csrc/attention/attention_kernels.cuh:252-253).
+ *   - All strides are in ELEMENTS of the tensor they describe.
+ */
+#ifndef B200PA_H_
+#define B200PA_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200PA_VERSION 1
+
+/* Error codes (negative). */
+#define B200PA_OK 0
+#define B200PA_EINVAL (-1)      /* bad argument (null pointer, bad size, bad stride)     */
+#define B200PA_EUNSUPPORTED (-2)/* head size / block size / dtype combination not built  */
+#define B200PA_ECUDA (-3)       /* a CUDA runtime call failed at launch time             */
+#define B200PA_EDEVICE (-4)     /* a kernel reported a bounded wait that ran out         */
+
+/* Element type of query / out / key / value (the reference dispatches on
+ * at::ScalarType Float / Half / BFloat16, quant_utils.cuh:545-593). */
+typedef enum b200pa_dtype {
+  B200PA_F32 = 0,
+  B200PA_F16 = 1,
+  B200PA_BF16 = 2
+} b200pa_dtype;
+
+/* Storage type of the paged KV cache; the reference passes this as the string
+ * kv_cache_dtype ("auto" | "fp8" | "fp8_e4m3" | "fp8_e5m2" | "fp8_ds_mla"). */
+typedef enum b200pa_kv_dtype {
+  B200PA_KV_AUTO = 0,     /* cache holds the same 16/32-bit type as query/key */
+  B200PA_KV_FP8_E4M3 = 1, /* 1 byte per element, OCP e4m3fn                   */
+  B200PA_KV_FP8_E5M2 = 2  /* 1 byte per element, e5m2                         */
+} b200pa_kv_dtype;
+
+/* Maps the reference's kv_cache_dtype string to b200pa_kv_dtype
+ * (DISPATCH_BY_KV_CACHE_DTYPE, quant_utils.cuh:545-593); -1 if unknown. */
+int b200pa_kv_dtype_from_string(const char* kv_cache_dtype);
+
+/*
+ * Arguments of paged_attention_v1 / paged_attention_v2.
+ * Replaces: csrc/ops.h:32-53, launchers csrc/attention/paged_attention_v1.cu:43-125
+ * and paged_attention_v2.cu:43-131.
+ *
+ * Layouts (x = 16 / sizeof(cache element)):
+ *   out          [num_seqs, num_heads, head_size]               contiguous
+ *   query        [num_seqs, num_heads, head_size]               row stride q_stride
+ *   key_cache    [num_blocks, num_kv_heads, head_size/x, block_size, x]
+ *   value_cache  [num_blocks, num_kv_heads, head_size, block_size]
+ *                block stride kv_block_stride, head stride kv_head_stride
+ *                (K's strides address V too, as in the reference)
+ *   block_tables [num_seqs, max_num_blocks_per_seq] int32
+ *   seq_lens     [num_seqs] int32
+ *   alibi_slopes [num_heads] float32 or NULL
+ *   k_scale, v_scale : device pointers to ONE float each (may be NULL when
+ *                kv_dtype == B200PA_KV_AUTO)
+ * v2 scratch, owned by the caller, contents unspecified after the call:
+ *   exp_sums, max_logits [num_seqs, num_heads, max_num_partitions] float32
+ *   tmp_out              [num_seqs, num_heads, max_num_partitions, head_size] (query dtype)
+ *   max_num_partitions = ceil(max_seq_len / 512)
+ */
+typedef struct b200pa_attn_args {
+  void* out;
+  const void* query;
+  const void* key_cache;
+  const void* value_cache;
+  const int32_t* block_tables;
+  const int32_t* seq_lens;
+  const float* alibi_slopes;
+  const float* k_scale;
+  const float* v_scale;
+  float* exp_sums;
+  float* max_logits;
+  void* tmp_out;
+
+  int64_t q_stride;
+  int64_t kv_block_stride;
+  int64_t kv_head_stride;
+
+  int32_t num_seqs;
+  int32_t num_heads;
+  int32_t num_kv_heads;
+  int32_t head_size;
+  int32_t block_size;
+  int32_t max_seq_len;
+  int32_t max_num_blocks_per_seq;
+  int32_t max_num_partitions; /* v2 only; ignored by v1 */
+
+  float scale;
+  int32_t q_dtype;  /* b200pa_dtype    */
+  int32_t kv_dtype; /* b200pa_kv_dtype */
+
+  /* Block-sparse arguments of the reference signature.  Only the dense case
+   * (blocksparse_vert_stride <= 1) is implemented; anything else returns
+   * B200PA_EUNSUPPORTED. */
+  int32_t tp_rank;
+  int32_t blocksparse_local_blocks;
+  int32_t blocksparse_vert_stride;
+  int32_t blocksparse_block_size;
+  int32_t blocksparse_head_sliding_step;
+} b200pa_attn_args;
+
+/* Replaces paged_attention_v1 (csrc/attention/paged_attention_v1.cu:160-182):
+ * whole sequence per work item, no scratch. */
+int b200pa_paged_attention_v1(const b200pa_attn_args* args, void* stream);
+
+/* Replaces paged_attention_v2 + its reduce kernel
+ * (csrc/attention/paged_attention_v2.cu:167-192, attention_kernels.cuh:559-664):
+ * split-KV over 512-token partitions using the caller's scratch. */
+int b200pa_paged_attention_v2(const b200pa_attn_args* args, void* stream);
+
+/*
+ * Arguments of reshape_and_cache / reshape_and_cache_flash.
+ * Replaces: csrc/cache.h:21-32, launchers csrc/cache_kernels.cu:656-683 and :700-738.
+ *
+ *   key, value   [num_tokens, num_heads, head_size]  row strides key_stride/value_stride
+ *   slot_mapping [num_tokens] int64; slot < 0 = padded token, skipped
+ * reshape_and_cache ("x-layout", contiguous caches):
+ *   key_cache    [num_blocks, num_heads, head_size/x, block_size, x]
+ *   value_cache  [num_blocks, num_heads, head_size, block_size]
+ *   (x is given explicitly, as the reference reads it from key_cache.size(4))
+ * reshape_and_cache_flash (strided caches, NHD or HND):
+ *   key_cache/value_cache viewed as [num_blocks, block_size, num_heads, head_size]
+ *   with element strides (block_stride, page_stride, head_stride).
+ * fp8: bits = cvt_rn_satfinite(float(v) / scale) with IEEE division
+ *   (quant_utils.cuh:469-502).
+ */
+typedef struct b200pa_cache_args {
+  const void* key;
+  const void* value;
+  void* key_cache;
+  void* value_cache;
+  const int64_t* slot_mapping;
+  const float* k_scale;
+  const float* v_scale;
+
+  int64_t key_stride;
+  int64_t value_stride;
+  int64_t block_stride; /* flash only */
+  int64_t page_stride;  /* flash only */
+  int64_t head_stride;  /* flash only */
+
+  int32_t num_tokens;
+  int32_t num_heads;
+  int32_t head_size;
+  int32_t block_size;
+  int32_t x;        /* x-layout only */
+  int32_t in_dtype; /* b200pa_dtype    */
+  int32_t kv_dtype; /* b200pa_kv_dtype */
+} b200pa_cache_args;
+
+int b200pa_reshape_and_cache(const b200pa_cache_args* args, void* stream);
+int b200pa_reshape_and_cache_flash(const b200pa_cache_args* args, void* stream);
+
+/*
+ * Replaces convert_fp8 (csrc/cache_kernels.cu:826-899): elementwise
+ * quantise (src 16/32-bit -> dst fp8) or dequantise (src fp8 -> dst 16/32-bit)
+ * of `numel` contiguous elements with a host-side scalar scale.
+ * wide_dtype is the b200pa_dtype of the non-fp8 side; kv_dtype selects e4m3/e5m2.
+ * to_fp8 != 0: dst is fp8.
+ */
+int b200pa_convert_fp8(void* dst, const void* src, int64_t numel, float scale,
+                       int32_t wide_dtype, int32_t kv_dtype, int32_t to_fp8,
+                       void* stream);
+
+/* Thread-local message for the last non-zero return on this thread ("" if none). */
+const char* b200pa_last_error(void);
+
+/* B200PA_VERSION of the loaded library. */
+int b200pa_version(void);
+
+/*
+ * Reads (and clears) the device-side status word of the current device.  The
+ * decode kernel's mbarrier waits are bounded; a wait that runs out records a
+ * code here and the kernel returns instead of spinning.  This call synchronises
+ * the device; it is meant for tests and debugging, never for the hot path.
+ * Returns 0 and stores the word (0 = healthy) in *status.
+ */
+int b200pa_device_status(int32_t* status);
+
+/* Number of kernel launches issued by this library on the calling thread since
+ * the last call with reset != 0 (host-side counter, for benchmark bookkeeping). */
+int64_t b200pa_launch_count(int reset);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+
+#endif /* B200PA_H_ */

@@ -1,0 +1,230 @@
+"""CPU oracle for the PagedAttention decode path.  TEST INFRASTRUCTURE ONLY.
+
+A PyTorch-on-CPU restatement of what the reference's CUDA kernels compute, used
+as the checker in ``tests/``, in ``__graft_entry__.smoke()`` and as the "port"
+CPU baseline of ``bench.py``.  The product never imports this module.
+
+What each function follows in the reference:
+
+``quantize_fp8`` / ``dequantize_fp8``
+    ``fp8::scaled_convert`` — csrc/quantization/w8a8/fp8/nvidia/quant_utils.cuh:469-502
+    (quantise: IEEE fp32 division, cvt round-to-nearest-even, saturate-to-finite,
+    NaN -> 0x7F) and :360-372 (dequantise: fp8 -> half -> float * scale -> T).
+``reshape_and_cache`` / ``reshape_and_cache_flash``
+    csrc/cache_kernels.cu:225-283 and :285-358 (index formulas, ``slot < 0`` skipped).
+``paged_attention`` (mode="ref")
+    csrc/attention/attention_kernels.cuh:81-491 with its rounding points: fp32
+    logits, ``exp`` softmax with ``1/(sum + 1e-6)``, P rounded to the value dtype,
+    the P*V product formed in that dtype, fp32 accumulation; with
+    ``partition_size`` the v2 split (:106-131, :344-352) and the reduce kernel
+    (:559-664) including the rounding of the partial outputs to T.
+``paged_attention`` (mode="f64")
+    the same mathematics in float64 without intermediate rounding
+    (tests/kernels/attention/test_attention.py:47-114 is the PyTorch statement).
+
+Pinning: the quantiser is checked bit-for-bit against golden vectors produced by
+NVIDIA's host ``__nv_cvt_float_to_fp8`` (tests/golden/fp8_*.npz); attention is
+checked against outputs of the reference's own CPU attention kernel
+(tests/golden/cpu_attn_*.npz) and, on a GPU box, against the reference's CUDA
+kernels compiled from its sources (oracle/_ref/_C_ref.so).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+FP8_FORMATS = {
+    "fp8": (torch.float8_e4m3fn, 448.0),
+    "fp8_e4m3": (torch.float8_e4m3fn, 448.0),
+    "fp8_ds_mla": (torch.float8_e4m3fn, 448.0),
+    "fp8_e5m2": (torch.float8_e5m2, 57344.0),
+}
+
+
+def is_fp8(kv_cache_dtype: str) -> bool:
+    if kv_cache_dtype == "auto":
+        return False
+    if kv_cache_dtype not in FP8_FORMATS:
+        raise RuntimeError(f"Unsupported data type of kv cache: {kv_cache_dtype}")
+    return True
+
+
+def quantize_fp8(x: torch.Tensor, scale: float, kv_cache_dtype: str = "fp8") -> torch.Tensor:
+    """bits = cvt_rn_satfinite(float(x) / scale) as uint8 (NaN -> 0x7F)."""
+    dt, fmax = FP8_FORMATS[kv_cache_dtype]
+    q = x.to(torch.float32) / torch.tensor(scale, dtype=torch.float32)
+    bits = q.clamp(-fmax, fmax).to(dt).view(torch.uint8).clone()
+    bits[q.isnan()] = 0x7F
+    return bits
+
+
+def dequantize_fp8(bits: torch.Tensor, scale: float, out_dtype: torch.dtype,
+                   kv_cache_dtype: str = "fp8") -> torch.Tensor:
+    """T(float(half(fp8)) * scale): every fp8 value is exact in half."""
+    dt, _ = FP8_FORMATS[kv_cache_dtype]
+    f = bits.view(dt).to(torch.float32) * torch.tensor(scale, dtype=torch.float32)
+    return f.to(out_dtype)
+
+
+def _scalar(t) -> float:
+    return float(t.item()) if isinstance(t, torch.Tensor) else float(t)
+
+
+def reshape_and_cache(key, value, key_cache, value_cache, slot_mapping, kv_cache_dtype,
+                      k_scale, v_scale) -> None:
+    """x-layout KV write: K -> [b, h, d/x, t, d%x], V -> [b, h, d, t] (in place)."""
+    num_tokens = slot_mapping.shape[0]
+    block_size = key_cache.shape[3]
+    x = key_cache.shape[4]
+    H, D = key.shape[1], key.shape[2]
+    slots = slot_mapping.to(torch.int64)
+    keep = slots >= 0
+    idx = torch.nonzero(keep).flatten()
+    if idx.numel() == 0:
+        return
+    k = key[:num_tokens][idx]
+    v = value[:num_tokens][idx]
+    if is_fp8(kv_cache_dtype):
+        k = quantize_fp8(k, _scalar(k_scale), kv_cache_dtype)
+        v = quantize_fp8(v, _scalar(v_scale), kv_cache_dtype)
+        kc = key_cache.view(torch.uint8)
+        vc = value_cache.view(torch.uint8)
+    else:
+        kc, vc = key_cache, value_cache
+    b = torch.div(slots[idx], block_size, rounding_mode="floor")
+    t = slots[idx] % block_size
+    kc[b, :, :, t, :] = k.reshape(-1, H, D // x, x)
+    vc[b, :, :, t] = v
+
+
+def reshape_and_cache_flash(key, value, key_cache, value_cache, slot_mapping, kv_cache_dtype,
+                            k_scale, v_scale) -> None:
+    """flash-layout KV write into [num_blocks, block_size, H, D] views (any strides)."""
+    num_tokens = slot_mapping.shape[0]
+    block_size = key_cache.shape[1]
+    slots = slot_mapping.to(torch.int64)
+    idx = torch.nonzero(slots >= 0).flatten()
+    if idx.numel() == 0:
+        return
+    k = key[:num_tokens][idx]
+    v = value[:num_tokens][idx]
+    if is_fp8(kv_cache_dtype):
+        k = quantize_fp8(k, _scalar(k_scale), kv_cache_dtype)
+        v = quantize_fp8(v, _scalar(v_scale), kv_cache_dtype)
+        kc = key_cache.view(torch.uint8)
+        vc = value_cache.view(torch.uint8)
+    else:
+        kc, vc = key_cache, value_cache
+    b = torch.div(slots[idx], block_size, rounding_mode="floor")
+    t = slots[idx] % block_size
+    kc[b, t] = k
+    vc[b, t] = v
+
+
+def gather_kv(key_cache, value_cache, block_table, seq_len, kv_cache_dtype, k_scale, v_scale,
+              work_dtype):
+    """Returns K, V of one sequence as [seq_len, Hkv, D] tensors of ``work_dtype``
+    (fp8 caches dequantised with the reference's rounding to the query dtype)."""
+    B = value_cache.shape[3]
+    nblk = (seq_len + B - 1) // B
+    blocks = block_table[:nblk].to(torch.int64)
+    kc = key_cache[blocks]    # [nblk, H, D/x, B, x]
+    vc = value_cache[blocks]  # [nblk, H, D, B]
+    nb, H, Dx, _, x = kc.shape
+    k = kc.permute(0, 3, 1, 2, 4).reshape(nb * B, H, Dx * x)[:seq_len]
+    v = vc.permute(0, 3, 1, 2).reshape(nb * B, H, -1)[:seq_len]
+    if is_fp8(kv_cache_dtype):
+        k = dequantize_fp8(k.contiguous().view(torch.uint8), _scalar(k_scale), work_dtype, kv_cache_dtype)
+        v = dequantize_fp8(v.contiguous().view(torch.uint8), _scalar(v_scale), work_dtype, kv_cache_dtype)
+    return k, v
+
+
+def _attend_ref(q, k, v, scale, slopes, seq_len, tok0, T):
+    """One (sequence, token range) with the reference's rounding points.
+    q [Hq, D] (T), k/v [n, Hq, D] (T).  Returns (out fp32 [Hq, D] normalised, m [Hq], l [Hq])."""
+    n = k.shape[0]
+    logits = torch.einsum("hd,nhd->hn", q.float(), k.float()) * scale
+    if slopes is not None:
+        pos = torch.arange(tok0, tok0 + n, dtype=torch.float32) - seq_len + 1
+        logits = logits + slopes.view(-1, 1).float() * pos.view(1, -1)
+    m = logits.max(dim=1).values
+    e = torch.exp(logits - m.view(-1, 1))
+    l = e.sum(dim=1)
+    p = e * (1.0 / (l + 1e-6)).view(-1, 1)
+    p_t = p.to(T)
+    prod = (p_t.float().transpose(0, 1).unsqueeze(-1) * v.float()).to(T)  # product formed in T
+    out = prod.float().sum(dim=0)
+    return out, m, l
+
+
+def paged_attention(query, key_cache, value_cache, num_kv_heads, scale, block_tables, seq_lens,
+                    alibi_slopes=None, kv_cache_dtype="auto", k_scale=1.0, v_scale=1.0,
+                    mode="ref", partition_size=None, seqs=None):
+    """Decode attention over a paged KV cache; returns ``out`` [S, Hq, D].
+
+    mode="ref": reference rounding points, result in the query dtype.
+    mode="f64": float64 mathematics, result in float64.
+    partition_size: None = one pass per sequence (v1); an int = v2 split + reduce.
+    seqs: optional iterable of sequence indices to compute (others are left zero).
+    """
+    S, Hq, D = query.shape
+    G = Hq // num_kv_heads
+    T = query.dtype
+    out = torch.zeros((S, Hq, D), dtype=torch.float64 if mode == "f64" else T)
+    lens = seq_lens.tolist()
+    for s in (range(S) if seqs is None else seqs):
+        L = int(lens[s])
+        if L == 0:
+            continue
+        # mode "f64" dequantises fp8 exactly (no rounding to T)
+        work = torch.float32 if mode == "f64" else T
+        k, v = gather_kv(key_cache, value_cache, block_tables[s], L, kv_cache_dtype, k_scale,
+                         v_scale, work)
+        if G > 1:
+            k = k.repeat_interleave(G, dim=1)
+            v = v.repeat_interleave(G, dim=1)
+        q = query[s]
+        if mode == "f64":
+            logits = torch.einsum("hd,nhd->hn", q.double(), k.double()) * scale
+            if alibi_slopes is not None:
+                pos = torch.arange(L, dtype=torch.float64) - L + 1
+                logits = logits + alibi_slopes.view(-1, 1).double() * pos.view(1, -1)
+            p = torch.softmax(logits, dim=1)
+            out[s] = torch.einsum("hn,nhd->hd", p, v.double())
+            continue
+        if partition_size is None:
+            o, _, _ = _attend_ref(q, k, v, scale, alibi_slopes, L, 0, T)
+            out[s] = o.to(T)
+            continue
+        nparts = (L + partition_size - 1) // partition_size
+        if nparts == 1:
+            # the reduce kernel copies the single partial through (:577-589)
+            o, _, _ = _attend_ref(q, k, v, scale, alibi_slopes, L, 0, T)
+            out[s] = o.to(T)
+            continue
+        tmp, ms, ls = [], [], []
+        for j in range(nparts):
+            a, b = j * partition_size, min(L, (j + 1) * partition_size)
+            o, m, l = _attend_ref(q, k[a:b], v[a:b], scale, alibi_slopes, L, a, T)
+            tmp.append(o.to(T))
+            ms.append(m)
+            ls.append(l)
+        tmp = torch.stack(tmp, 0).float()       # [P, Hq, D]
+        ms = torch.stack(ms, 0)                 # [P, Hq]
+        ls = torch.stack(ls, 0)
+        M = ms.max(dim=0).values
+        r = ls * torch.exp(ms - M.view(1, -1))
+        inv = 1.0 / (r.sum(dim=0) + 1e-6)
+        out[s] = (tmp * r.unsqueeze(-1) * inv.view(1, -1, 1)).sum(dim=0).to(T)
+    return out
+
+
+def attn_bytes(seq_lens, num_heads, num_kv_heads, head_size, block_size, q_bytes, cache_bytes):
+    """Algorithmic bytes of one decode call: KV read once (GQA-shared) + Q read +
+    O write + block-table entries + seq_lens."""
+    lens = [int(v) for v in seq_lens]
+    kv = sum(lens) * num_kv_heads * head_size * 2 * cache_bytes
+    qo = 2 * len(lens) * num_heads * head_size * q_bytes
+    bt = 4 * sum((n + block_size - 1) // block_size for n in lens) + 4 * len(lens)
+    return kv + qo + bt

@@ -1,0 +1,125 @@
+"""Operator wrappers with the reference's names, argument order and error behaviour.
+
+Mirror of ``vllm/_custom_ops.py:29-120`` (``paged_attention_v1/v2``) and
+``:2121-2199`` (``reshape_and_cache``, ``reshape_and_cache_flash``,
+``convert_fp8``) of the reference.  Each function is a pass-through to a torch
+custom op whose CUDA implementation lives in ``libb200pa.so``; loading this
+module loads the native libraries and raises if they are missing.
+"""
+from __future__ import annotations
+
+from pathlib import Path
+
+import torch
+
+_PKG = Path(__file__).resolve().parent
+_SHIM = _PKG / "_C_b200.so"
+
+
+def _load() -> None:
+    if not _SHIM.exists() or not (_PKG / "libb200pa.so").exists():
+        raise RuntimeError(
+            f"native libraries are missing under {_PKG}: run `python -m vllm_b200.build` "
+            "(there is no CPU or PyTorch fallback for these ops)")
+    torch.ops.load_library(str(_SHIM))
+
+
+_load()
+
+# Always-present private namespaces; `torch.ops._C.*` / `torch.ops._C_cache_ops.*`
+# resolve to the same kernels unless another library defined those names first.
+_ops = torch.ops._C_b200
+_cache_ops = torch.ops._C_b200_cache_ops
+
+
+def paged_attention_v1(
+    out: torch.Tensor,
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    num_kv_heads: int,
+    scale: float,
+    block_tables: torch.Tensor,
+    seq_lens: torch.Tensor,
+    block_size: int,
+    max_seq_len: int,
+    alibi_slopes: torch.Tensor | None,
+    kv_cache_dtype: str,
+    k_scale: torch.Tensor,
+    v_scale: torch.Tensor,
+    tp_rank: int = 0,
+    blocksparse_local_blocks: int = 0,
+    blocksparse_vert_stride: int = 0,
+    blocksparse_block_size: int = 64,
+    blocksparse_head_sliding_step: int = 0,
+) -> None:
+    _ops.paged_attention_v1(
+        out, query, key_cache, value_cache, num_kv_heads, scale, block_tables, seq_lens,
+        block_size, max_seq_len, alibi_slopes, kv_cache_dtype, k_scale, v_scale, tp_rank,
+        blocksparse_local_blocks, blocksparse_vert_stride, blocksparse_block_size,
+        blocksparse_head_sliding_step)
+
+
+def paged_attention_v2(
+    out: torch.Tensor,
+    exp_sum: torch.Tensor,
+    max_logits: torch.Tensor,
+    tmp_out: torch.Tensor,
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    num_kv_heads: int,
+    scale: float,
+    block_tables: torch.Tensor,
+    seq_lens: torch.Tensor,
+    block_size: int,
+    max_seq_len: int,
+    alibi_slopes: torch.Tensor | None,
+    kv_cache_dtype: str,
+    k_scale: torch.Tensor,
+    v_scale: torch.Tensor,
+    tp_rank: int = 0,
+    blocksparse_local_blocks: int = 0,
+    blocksparse_vert_stride: int = 0,
+    blocksparse_block_size: int = 64,
+    blocksparse_head_sliding_step: int = 0,
+) -> None:
+    _ops.paged_attention_v2(
+        out, exp_sum, max_logits, tmp_out, query, key_cache, value_cache, num_kv_heads, scale,
+        block_tables, seq_lens, block_size, max_seq_len, alibi_slopes, kv_cache_dtype, k_scale,
+        v_scale, tp_rank, blocksparse_local_blocks, blocksparse_vert_stride,
+        blocksparse_block_size, blocksparse_head_sliding_step)
+
+
+def reshape_and_cache(
+    key: torch.Tensor,
+    value: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    slot_mapping: torch.Tensor,
+    kv_cache_dtype: str,
+    k_scale: torch.Tensor,
+    v_scale: torch.Tensor,
+) -> None:
+    _cache_ops.reshape_and_cache(
+        key, value, key_cache, value_cache, slot_mapping, kv_cache_dtype, k_scale, v_scale)
+
+
+def reshape_and_cache_flash(
+    key: torch.Tensor,
+    value: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    slot_mapping: torch.Tensor,
+    kv_cache_dtype: str,
+    k_scale: torch.Tensor,
+    v_scale: torch.Tensor,
+) -> None:
+    _cache_ops.reshape_and_cache_flash(
+        key, value, key_cache, value_cache, slot_mapping, kv_cache_dtype, k_scale, v_scale)
+
+
+def convert_fp8(
+    output: torch.Tensor, input: torch.Tensor, scale: float = 1.0, kv_dtype: str = "fp8"
+) -> None:
+    _cache_ops.convert_fp8(output, input, scale, kv_dtype)

@@ -1,0 +1,584 @@
+// Persistent split-KV decode kernel (the hot loop of paged_attention_v1/v2).
+// Replaces the reference's paged_attention_kernel
+// (csrc/attention/attention_kernels.cuh:81-491).
+//
+// Design (bandwidth first; the KV cache is read exactly once):
+//   * One persistent CTA per SM.  Every WARP is an independent worker: it pulls a
+//     work item (sequence, kv head, 512-token partition) from a global ticket,
+//     streams that item's KV pages through its own ring of shared-memory stages
+//     and writes the item's result itself.  There is no CTA-wide barrier after
+//     set-up, and a warp keeps prefetching pages of its NEXT item while it
+//     finishes the current one, so the pipeline never drains.
+//   * A KV page (one block of one kv head) is contiguous in both cache layouts:
+//     K [D/x][B][x] and V [D][B].  Each is fetched with ONE 1-D bulk async copy
+//     (cp.async.bulk, completion on an mbarrier; no cluster multicast).
+//   * All query heads that share the kv head are processed together on the
+//     tensor cores with tokens on the M axis and heads on the 8-wide N axis
+//     (mma.sync m16n8k16, fp32 accumulate):
+//         S^T[16 tok x 8 heads] = K[16 tok x D] . Q^T          (A = K via ldmatrix)
+//         O^T[D x 8 heads]     += V^T[D x 16 tok] . P^T         (A = V via ldmatrix)
+//     The x-layout of K and the [D][B] layout of V are exactly the row-major A
+//     operands these products need, so pages are used as they land, untransposed.
+//     P^T is produced from the S^T accumulators with one movmatrix per 8 tokens.
+//   * fp8 caches are dequantised after ldmatrix (4 bytes per lane) with
+//     cvt.f16x2.e4m3x2; the dot-product index order inside a 16-wide k-step is
+//     permuted consistently in Q / P, which is free.  k_scale is folded into the
+//     logit scale and v_scale into the output scale.
+//   * Online softmax in the log2 domain, fp32 state, warp-shuffle reductions.
+//   * Every mbarrier wait is bounded; on expiry the warp records a status code
+//     and leaves.
+#pragma once
+
+#include <type_traits>
+
+#include "decode_common.cuh"
+
+namespace b200pa {
+
+enum : int { kCache16 = 0, kCacheE4M3 = 1, kCacheE5M2 = 2 };
+
+struct WorkItem {
+  int seq;
+  int kvh;
+  int hg;          // head group inside the kv head
+  int part;        // partition index inside the sequence
+  int nparts;      // partitions of this sequence (>= 1)
+  int tok_begin;
+  int tok_end;
+  int first_page;
+  int npages;
+  int win;         // which 32-page window `bt` holds
+  int bt;          // per-lane block id of page first_page + 32*win + lane
+  bool valid;
+};
+
+template <typename QT, int KV, int D, int GP>
+struct DecodeTraits {
+  static constexpr bool kFp8 = KV != kCache16;
+  static constexpr bool kMmaBf16 = !kFp8 && std::is_same_v<QT, __nv_bfloat16>;
+  static constexpr int kEsize = kFp8 ? 1 : 2;
+  static constexpr int kKSteps = D / 16;   // k-steps of QK / m-tiles of PV
+  static constexpr int kHeadsPerItem = 8 * GP;
+};
+
+// Reads this lane's block id for the 32-page window `win` of an item.
+__device__ __forceinline__ int load_bt(const DecodeParams& p, const WorkItem& it, int win, int lane) {
+  const int pg = win * 32 + lane;
+  if (pg >= it.npages) return 0;
+  return __ldg(p.block_tables + int64_t(it.seq) * p.max_blocks_per_seq + it.first_page + pg);
+}
+
+template <typename QT, int KV, int D, int GP>
+__global__ void __launch_bounds__(kMaxWarps * 32, 1) pa_decode_kernel(const DecodeParams p) {
+  using TR = DecodeTraits<QT, KV, D, GP>;
+  constexpr bool kFp8 = TR::kFp8;
+  constexpr bool kBf = TR::kMmaBf16;
+  constexpr int ES = TR::kEsize;
+  constexpr int KS = TR::kKSteps;
+  constexpr bool kE5 = KV == kCacheE5M2;
+  constexpr bool kOutBf = std::is_same_v<QT, __nv_bfloat16>;
+
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int nwarps = blockDim.x >> 5;
+  const int g = lane >> 2;  // fragment row group
+  const int c = lane & 3;   // fragment column pair
+  const int B = p.block_size;
+  const int NS = p.nstages;
+  const uint32_t page_bytes = uint32_t(D) * B * ES;
+  const uint32_t stage_bytes = 2 * page_bytes;
+
+  // ---- shared memory carve-up: [partition prefix table][mbarriers][stages]
+  int* cum = reinterpret_cast<int*>(smem_raw);
+  const int table_ints = p.use_table ? ((p.num_seqs + 1 + 3) & ~3) : 0;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + size_t(table_ints) * 4);
+  const uint32_t bars_bytes = (uint32_t(nwarps) * NS * 8 + 127u) & ~127u;
+  unsigned char* stages = smem_raw + size_t(table_ints) * 4 + bars_bytes;
+  // the dynamic buffer is 128-byte aligned and table_ints*4 is a multiple of 16
+  const uint32_t my_stage0 = smem_u32(stages) + uint32_t(warp) * NS * stage_bytes;
+  const uint32_t my_bar0 = smem_u32(bars) + uint32_t(warp) * NS * 8;
+
+  // ---- set-up: prefix table of partitions per sequence (exclusive scan)
+  if (p.use_table) {
+    __shared__ int warp_tot[kMaxWarps];
+    const int S = p.num_seqs;
+    const int per = (S + blockDim.x - 1) / blockDim.x;
+    const int s0 = min(S, int(threadIdx.x) * per);
+    const int s1 = min(S, s0 + per);
+    int mine = 0;
+    for (int s = s0; s < s1; ++s) {
+      const int len = p.seq_lens[s];
+      mine += max(1, (len + kPartitionTokens - 1) / kPartitionTokens);
+    }
+    int incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    int base = 0;
+    for (int w = 0; w < warp; ++w) base += warp_tot[w];
+    int run = base + incl - mine;
+    for (int s = s0; s < s1; ++s) {
+      cum[s] = run;
+      const int len = p.seq_lens[s];
+      run += max(1, (len + kPartitionTokens - 1) / kPartitionTokens);
+    }
+    if (threadIdx.x == blockDim.x - 1) cum[S] = run;
+  }
+  if (lane == 0) {
+    for (int s = 0; s < NS; ++s) mbar_init(my_bar0 + s * 8, 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+
+  const int hsubs = p.num_kv_heads * p.head_groups;
+  const int total_parts = p.use_table ? cum[p.num_seqs] : p.num_seqs;
+  const unsigned total_items = unsigned(total_parts) * unsigned(hsubs);
+  const uint64_t policy = policy_evict_first();
+  const char* kc_base = static_cast<const char*>(p.kc);
+  const char* vc_base = static_cast<const char*>(p.vc);
+
+  auto fetch = [&]() -> unsigned {
+    unsigned v = 0;
+    if (lane == 0) v = atomicAdd(p.sched, 1u);
+    return __shfl_sync(0xffffffffu, v, 0);
+  };
+
+  auto decode = [&](unsigned raw) -> WorkItem {
+    WorkItem it;
+    it.valid = raw < total_items;
+    it.seq = it.kvh = it.hg = it.part = it.tok_begin = it.tok_end = it.first_page = it.npages = 0;
+    it.nparts = 1;
+    it.win = 0;
+    it.bt = 0;
+    if (!it.valid) return it;
+    const int hsub = int(raw % unsigned(hsubs));
+    const int cg = int(raw / unsigned(hsubs));
+    it.kvh = hsub / p.head_groups;
+    it.hg = hsub % p.head_groups;
+    if (p.use_table) {
+      int lo = 0, hi = p.num_seqs;  // last s with cum[s] <= cg
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (cum[mid] <= cg) lo = mid; else hi = mid;
+      }
+      it.seq = lo;
+      it.part = cg - cum[lo];
+      it.nparts = cum[lo + 1] - cum[lo];
+      const int len = p.seq_lens[lo];
+      it.tok_begin = it.part * kPartitionTokens;
+      it.tok_end = min(len, it.tok_begin + kPartitionTokens);
+    } else {
+      it.seq = cg;
+      it.tok_begin = 0;
+      it.tok_end = p.seq_lens[cg];
+    }
+    if (it.tok_end < it.tok_begin) it.tok_end = it.tok_begin;
+    it.first_page = it.tok_begin / B;
+    it.npages = (it.tok_end - it.tok_begin + B - 1) / B;
+    it.bt = load_bt(p, it, 0, lane);
+    return it;
+  };
+
+  WorkItem cur = decode(fetch());
+  WorkItem nxt = decode(fetch());
+  unsigned nn_raw = fetch();
+
+  // ---- producer state
+  int prod_sel = 0;  // 0: producing pages of `cur`, 1: of `nxt`
+  int prod_pg = 0;
+  int prod_stage = 0;
+  int inflight = 0;
+  int cons_stage = 0;
+  uint32_t cons_phase = 0;
+
+  auto produce_one = [&]() -> bool {
+    if (prod_sel == 0 && prod_pg >= cur.npages) {
+      prod_sel = 1;
+      prod_pg = 0;
+    }
+    if (prod_sel == 1 && (!nxt.valid || prod_pg >= nxt.npages)) return false;
+    WorkItem& it = prod_sel ? nxt : cur;
+    const int win = prod_pg >> 5;
+    if (win != it.win) {
+      it.win = win;
+      it.bt = load_bt(p, it, win, lane);
+    }
+    const int blk = __shfl_sync(0xffffffffu, it.bt, prod_pg & 31);
+    if (lane == 0) {
+      const int64_t off = (int64_t(blk) * p.kv_block_stride + int64_t(it.kvh) * p.kv_head_stride) * ES;
+      const uint32_t bar = my_bar0 + prod_stage * 8;
+      const uint32_t dst = my_stage0 + prod_stage * stage_bytes;
+      mbar_expect_tx(bar, stage_bytes);
+      bulk_g2s(dst, kc_base + off, page_bytes, bar, policy);
+      bulk_g2s(dst + page_bytes, vc_base + off, page_bytes, bar, policy);
+    }
+    prod_stage = (prod_stage + 1 == NS) ? 0 : prod_stage + 1;
+    ++prod_pg;
+    ++inflight;
+    return true;
+  };
+
+  while (inflight < NS && produce_one()) {}
+
+  const float kv_qk = kFp8 ? *p.k_scale : 1.f;
+  const float kv_o = kFp8 ? *p.v_scale : 1.f;
+  const float qk_scale = p.scale * kLog2e * kv_qk;
+  bool failed = false;
+
+  while (cur.valid && !failed) {
+    const int hq0 = cur.kvh * p.group + cur.hg * TR::kHeadsPerItem;
+    const int nheads = min(TR::kHeadsPerItem, p.group - cur.hg * TR::kHeadsPerItem);
+    const int seq_len = p.seq_lens[cur.seq];
+
+    // ---- Q fragments (B operand), head = nt*8 + g
+    uint32_t qf[GP][KS][2];
+#pragma unroll
+    for (int nt = 0; nt < GP; ++nt) {
+      const int hl = nt * 8 + g;
+      const QT* qrow = static_cast<const QT*>(p.q) + int64_t(cur.seq) * p.q_stride +
+                       int64_t(hq0 + hl) * D;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        uint32_t v0 = 0, v1 = 0;
+        if (hl < nheads) {
+          if constexpr (!kFp8) {
+            v0 = *reinterpret_cast<const uint32_t*>(qrow + 16 * ks + 2 * c);
+            v1 = *reinterpret_cast<const uint32_t*>(qrow + 16 * ks + 8 + 2 * c);
+          } else {
+            // k index 2c+i <-> d 4c+i ; k index 2c+8+i <-> d 4c+2+i ; operands in f16
+            const uint2 raw = *reinterpret_cast<const uint2*>(qrow + 16 * ks + 4 * c);
+            const QT* e = reinterpret_cast<const QT*>(&raw);
+            v0 = pack2<false>(to_f32(e[0]), to_f32(e[1]));
+            v1 = pack2<false>(to_f32(e[2]), to_f32(e[3]));
+          }
+        }
+        qf[nt][ks][0] = v0;
+        qf[nt][ks][1] = v1;
+      }
+    }
+    float slope[GP][2];
+#pragma unroll
+    for (int nt = 0; nt < GP; ++nt)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int hl = nt * 8 + 2 * c + j;
+        slope[nt][j] = (p.alibi != nullptr && hl < nheads) ? p.alibi[hq0 + hl] * kLog2e : 0.f;
+      }
+
+    float o[KS][GP][4];
+#pragma unroll
+    for (int mt = 0; mt < KS; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < GP; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[mt][nt][i] = 0.f;
+    float m_run[GP][2], l_run[GP][2];
+#pragma unroll
+    for (int nt = 0; nt < GP; ++nt) {
+      m_run[nt][0] = m_run[nt][1] = -INFINITY;
+      l_run[nt][0] = l_run[nt][1] = 0.f;
+    }
+
+    for (int pg = 0; pg < cur.npages; ++pg) {
+      const uint32_t bar = my_bar0 + cons_stage * 8;
+      if (!__all_sync(0xffffffffu, mbar_wait(bar, cons_phase))) {
+        if (lane == 0) atomicExch(p.status, kStatusMbarTimeout);
+        failed = true;
+        break;
+      }
+      const uint32_t sk = my_stage0 + cons_stage * stage_bytes;
+      const uint32_t sv = sk + page_bytes;
+      const int page_tok0 = (cur.first_page + pg) * B;
+
+      // zero V columns of tokens past the end of the sequence (stale cache bytes
+      // could be NaN/Inf; the reference zeroes them too, attention_kernels.cuh:415-425)
+      if (page_tok0 + B > cur.tok_end) {
+        const int rem = cur.tok_end - page_tok0;
+        const int w = B - rem;
+        unsigned char* vpage = stages + size_t(warp) * NS * stage_bytes +
+                               size_t(cons_stage) * stage_bytes + page_bytes;
+        for (int idx = lane; idx < D * w; idx += 32) {
+          const int d = idx / w;
+          const int t = rem + idx % w;
+          if constexpr (ES == 1) vpage[d * B + t] = 0;
+          else reinterpret_cast<uint16_t*>(vpage)[d * B + t] = 0;
+        }
+        __syncwarp();
+      }
+
+      for (int tt = 0; tt < B; tt += 16) {
+        const int tile_tok0 = page_tok0 + tt;
+        if (tile_tok0 >= cur.tok_end) break;
+
+        // ---------------- S^T = K . Q^T
+        float s[GP][4];
+#pragma unroll
+        for (int nt = 0; nt < GP; ++nt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) s[nt][i] = 0.f;
+
+        if constexpr (!kFp8) {
+          const uint32_t kaddr =
+              sk + uint32_t((((lane >> 4)) * B + tt + ((lane >> 3) & 1) * 8 + (lane & 7)) * 16);
+#pragma unroll
+          for (int ks = 0; ks < KS; ++ks) {
+            uint32_t a0, a1, a2, a3;
+            ldsm_x4(kaddr + uint32_t(2 * ks * B * 16), a0, a1, a2, a3);
+#pragma unroll
+            for (int nt = 0; nt < GP; ++nt)
+              mma16816<kBf>(s[nt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
+          }
+        } else {
+          // A row rho of half h <-> token 4*(rho/2) + 2*h + rho%2
+          const int rho = lane & 7, hsel = (lane >> 3) & 1;
+          const int tok = 4 * (rho >> 1) + 2 * hsel + (rho & 1);
+          const uint32_t kaddr = sk + uint32_t(((lane >> 4) * B + tt + tok) * 16);
+#pragma unroll
+          for (int ks = 0; ks + 1 < KS; ks += 2) {
+            uint32_t r0, r1, r2, r3;
+            ldsm_x4(kaddr + uint32_t(ks * B * 16), r0, r1, r2, r3);
+            const uint32_t a0 = fp8x2_to_f16x2<kE5>(uint16_t(r0 & 0xffff));
+            const uint32_t a2 = fp8x2_to_f16x2<kE5>(uint16_t(r0 >> 16));
+            const uint32_t a1 = fp8x2_to_f16x2<kE5>(uint16_t(r1 & 0xffff));
+            const uint32_t a3 = fp8x2_to_f16x2<kE5>(uint16_t(r1 >> 16));
+            const uint32_t b0 = fp8x2_to_f16x2<kE5>(uint16_t(r2 & 0xffff));
+            const uint32_t b2 = fp8x2_to_f16x2<kE5>(uint16_t(r2 >> 16));
+            const uint32_t b1 = fp8x2_to_f16x2<kE5>(uint16_t(r3 & 0xffff));
+            const uint32_t b3 = fp8x2_to_f16x2<kE5>(uint16_t(r3 >> 16));
+#pragma unroll
+            for (int nt = 0; nt < GP; ++nt) {
+              mma16816<false>(s[nt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
+              mma16816<false>(s[nt], b0, b1, b2, b3, qf[nt][ks + 1][0], qf[nt][ks + 1][1]);
+            }
+          }
+          if constexpr (KS & 1) {
+            constexpr int ks = KS - 1;
+            uint32_t r0, r1;
+            // lanes 0-15 supply the addresses of the two matrices (lanes 16-31 ignored)
+            ldsm_x2(sk + uint32_t((ks * B + tt + tok) * 16), r0, r1);
+            const uint32_t a0 = fp8x2_to_f16x2<kE5>(uint16_t(r0 & 0xffff));
+            const uint32_t a2 = fp8x2_to_f16x2<kE5>(uint16_t(r0 >> 16));
+            const uint32_t a1 = fp8x2_to_f16x2<kE5>(uint16_t(r1 & 0xffff));
+            const uint32_t a3 = fp8x2_to_f16x2<kE5>(uint16_t(r1 >> 16));
+#pragma unroll
+            for (int nt = 0; nt < GP; ++nt)
+              mma16816<false>(s[nt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
+          }
+        }
+
+        // ---------------- scale, ALiBi, mask
+        int tok_lo, tok_hi;  // absolute token of accumulator rows g and g+8
+        if constexpr (!kFp8) {
+          tok_lo = tile_tok0 + g;
+          tok_hi = tile_tok0 + g + 8;
+        } else {
+          tok_lo = tile_tok0 + 4 * (g >> 1) + (g & 1);
+          tok_hi = tok_lo + 2;
+        }
+        const bool need_mask = tile_tok0 + 16 > cur.tok_end;
+#pragma unroll
+        for (int nt = 0; nt < GP; ++nt) {
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            float v_lo = s[nt][j] * qk_scale;
+            float v_hi = s[nt][2 + j] * qk_scale;
+            if (p.alibi != nullptr) {
+              v_lo += slope[nt][j] * float(tok_lo - seq_len + 1);
+              v_hi += slope[nt][j] * float(tok_hi - seq_len + 1);
+            }
+            if (need_mask) {
+              if (tok_lo >= cur.tok_end) v_lo = -INFINITY;
+              if (tok_hi >= cur.tok_end) v_hi = -INFINITY;
+            }
+            s[nt][j] = v_lo;
+            s[nt][2 + j] = v_hi;
+          }
+        }
+
+        // ---------------- online softmax (per head; heads 2c, 2c+1 of each n-tile)
+        float alpha[GP][2];
+        bool rescale = false;
+#pragma unroll
+        for (int nt = 0; nt < GP; ++nt) {
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            float tmax = fmaxf(s[nt][j], s[nt][2 + j]);
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 4));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 8));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 16));
+            const float m_old = m_run[nt][j];
+            const float m_new = fmaxf(m_old, tmax);
+            // m_new is finite here: every processed tile holds at least one valid token
+            alpha[nt][j] = fast_exp2(m_old - m_new);
+            rescale |= (m_new != m_old);
+            m_run[nt][j] = m_new;
+            const float p_lo = fast_exp2(s[nt][j] - m_new);
+            const float p_hi = fast_exp2(s[nt][2 + j] - m_new);
+            l_run[nt][j] = l_run[nt][j] * alpha[nt][j] + p_lo + p_hi;
+            s[nt][j] = p_lo;
+            s[nt][2 + j] = p_hi;
+          }
+        }
+        if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+          for (int mt = 0; mt < KS; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < GP; ++nt) {
+              o[mt][nt][0] *= alpha[nt][0];
+              o[mt][nt][1] *= alpha[nt][1];
+              o[mt][nt][2] *= alpha[nt][0];
+              o[mt][nt][3] *= alpha[nt][1];
+            }
+        }
+
+        // ---------------- P^T as B operand
+        uint32_t pf[GP][2];
+#pragma unroll
+        for (int nt = 0; nt < GP; ++nt) {
+          pf[nt][0] = movm_trans(pack2<kBf>(s[nt][0], s[nt][1]));
+          pf[nt][1] = movm_trans(pack2<kBf>(s[nt][2], s[nt][3]));
+        }
+
+        // ---------------- O^T += V^T . P^T
+        if constexpr (!kFp8) {
+          const uint32_t vaddr =
+              sv + uint32_t(((((lane >> 3) & 1) * 8 + (lane & 7)) * B + tt + (lane >> 4) * 8) * 2);
+#pragma unroll
+          for (int mt = 0; mt < KS; ++mt) {
+            uint32_t a0, a1, a2, a3;
+            ldsm_x4(vaddr + uint32_t(16 * mt * B * 2), a0, a1, a2, a3);
+#pragma unroll
+            for (int nt = 0; nt < GP; ++nt)
+              mma16816<kBf>(o[mt][nt], a0, a1, a2, a3, pf[nt][0], pf[nt][1]);
+          }
+        } else {
+          const uint32_t vaddr =
+              sv + uint32_t((16 * (lane >> 4) + ((lane >> 3) & 1) * 8 + (lane & 7)) * B + tt);
+#pragma unroll
+          for (int mt = 0; mt + 1 < KS; mt += 2) {
+            uint32_t r0, r1, r2, r3;
+            ldsm_x4(vaddr + uint32_t(16 * mt * B), r0, r1, r2, r3);
+            const uint32_t a0 = fp8x2_to_f16x2<kE5>(uint16_t(r0 & 0xffff));
+            const uint32_t a2 = fp8x2_to_f16x2<kE5>(uint16_t(r0 >> 16));
+            const uint32_t a1 = fp8x2_to_f16x2<kE5>(uint16_t(r1 & 0xffff));
+            const uint32_t a3 = fp8x2_to_f16x2<kE5>(uint16_t(r1 >> 16));
+            const uint32_t b0 = fp8x2_to_f16x2<kE5>(uint16_t(r2 & 0xffff));
+            const uint32_t b2 = fp8x2_to_f16x2<kE5>(uint16_t(r2 >> 16));
+            const uint32_t b1 = fp8x2_to_f16x2<kE5>(uint16_t(r3 & 0xffff));
+            const uint32_t b3 = fp8x2_to_f16x2<kE5>(uint16_t(r3 >> 16));
+#pragma unroll
+            for (int nt = 0; nt < GP; ++nt) {
+              mma16816<false>(o[mt][nt], a0, a1, a2, a3, pf[nt][0], pf[nt][1]);
+              mma16816<false>(o[mt + 1][nt], b0, b1, b2, b3, pf[nt][0], pf[nt][1]);
+            }
+          }
+          if constexpr (KS & 1) {
+            constexpr int mt = KS - 1;
+            uint32_t r0, r1;
+            ldsm_x2(sv + uint32_t((16 * mt + ((lane >> 3) & 1) * 8 + (lane & 7)) * B + tt), r0, r1);
+            const uint32_t a0 = fp8x2_to_f16x2<kE5>(uint16_t(r0 & 0xffff));
+            const uint32_t a2 = fp8x2_to_f16x2<kE5>(uint16_t(r0 >> 16));
+            const uint32_t a1 = fp8x2_to_f16x2<kE5>(uint16_t(r1 & 0xffff));
+            const uint32_t a3 = fp8x2_to_f16x2<kE5>(uint16_t(r1 >> 16));
+#pragma unroll
+            for (int nt = 0; nt < GP; ++nt)
+              mma16816<false>(o[mt][nt], a0, a1, a2, a3, pf[nt][0], pf[nt][1]);
+          }
+        }
+      }  // tiles of the page
+
+      // ---- release the stage and refill it
+      __syncwarp();
+      if (page_tok0 + B > cur.tok_end) fence_proxy_async();  // generic writes above vs. the next bulk copy
+      cons_stage = (cons_stage + 1 == NS) ? 0 : cons_stage + 1;
+      if (cons_stage == 0) cons_phase ^= 1;
+      --inflight;
+      produce_one();
+    }  // pages
+    if (failed) break;
+
+    // ---- finalise the item: l over the 8 row groups, normalise, write
+    const bool direct = cur.nparts == 1;
+    QT* obase;
+    int64_t ohead_stride;
+    if (direct) {
+      obase = static_cast<QT*>(p.out) + (int64_t(cur.seq) * p.num_heads + hq0) * D;
+      ohead_stride = D;
+    } else {
+      obase = static_cast<QT*>(p.tmp_out) +
+              ((int64_t(cur.seq) * p.num_heads + hq0) * p.max_partitions + cur.part) * D;
+      ohead_stride = int64_t(p.max_partitions) * D;
+    }
+#pragma unroll
+    for (int nt = 0; nt < GP; ++nt) {
+      float inv[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        float l = l_run[nt][j];
+        l += __shfl_xor_sync(0xffffffffu, l, 4);
+        l += __shfl_xor_sync(0xffffffffu, l, 8);
+        l += __shfl_xor_sync(0xffffffffu, l, 16);
+        inv[j] = kv_o * __fdividef(1.f, l + 1e-6f);
+        const int hl = nt * 8 + 2 * c + j;
+        if (!direct && g == 0 && hl < nheads) {
+          const int64_t idx =
+              (int64_t(cur.seq) * p.num_heads + hq0 + hl) * p.max_partitions + cur.part;
+          p.max_logits[idx] = m_run[nt][j];
+          p.exp_sums[idx] = l;
+        }
+      }
+      const int hl_t = nt * 8 + g;  // head owned after the transpose
+#pragma unroll
+      for (int mt = 0; mt < KS; ++mt) {
+        // transposes are warp-collective: executed by all lanes, stores predicated
+        const uint32_t lo = movm_trans(pack2<kOutBf>(o[mt][nt][0] * inv[0],
+                                                                      o[mt][nt][1] * inv[1]));
+        const uint32_t hi = movm_trans(pack2<kOutBf>(o[mt][nt][2] * inv[0],
+                                                                      o[mt][nt][3] * inv[1]));
+        if (hl_t < nheads) {
+          QT* orow = obase + hl_t * ohead_stride + 16 * mt + 2 * c;
+          *reinterpret_cast<uint32_t*>(orow) = lo;
+          *reinterpret_cast<uint32_t*>(orow + 8) = hi;
+        }
+      }
+    }
+
+    // ---- advance to the next item
+    cur = nxt;
+    nxt = decode(nn_raw);
+    nn_raw = fetch();
+    if (prod_sel == 1) prod_sel = 0; else prod_pg = 0;
+    while (inflight < NS && produce_one()) {}
+  }
+
+  if (failed) {
+    // give copies already in flight a bounded chance to land before the CTA's
+    // shared memory is released
+    for (int i = 0; i < inflight; ++i) {
+      const uint32_t bar = my_bar0 + cons_stage * 8;
+      mbar_wait(bar, cons_phase);
+      cons_stage = (cons_stage + 1 == NS) ? 0 : cons_stage + 1;
+      if (cons_stage == 0) cons_phase ^= 1;
+    }
+  }
+
+  // ---- last CTA out re-arms the scheduler words for the next launch
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned prev = atomicAdd(p.sched + 1, 1u);
+    if (prev == gridDim.x - 1) {
+      p.sched[0] = 0;
+      p.sched[1] = 0;
+      __threadfence();
+    }
+  }
+}
+
+}  // namespace b200pa

@@ -1,0 +1,439 @@
+// Host entry points of paged_attention_v1 / v2, the split-KV reduce kernel and
+// the generic (any dtype / head size / block size) SIMT decode kernel.
+//
+// Replaces: csrc/attention/paged_attention_v1.cu:160-182, paged_attention_v2.cu:167-192
+// (host entries and launchers) and attention_kernels.cuh:559-664 (reduce) of the
+// reference.
+#include <algorithm>
+#include <atomic>
+#include <cstdlib>
+#include <iterator>
+
+#include "decode_inst.cuh"
+
+namespace b200pa {
+
+// ------------------------------------------------------------------ reduce
+// out[s,h,:] = sum_j tmp_out[s,h,j,:] * w_j / (sum_j w_j + 1e-6),
+// w_j = l_j * 2^(m_j - max_j m_j); one warp per (sequence, head).
+// Sequences with <= 1 partition were written to `out` by the decode kernel.
+template <typename QT>
+__global__ void pa_reduce_kernel(QT* __restrict__ out, const QT* __restrict__ tmp_out,
+                                 const float* __restrict__ exp_sums,
+                                 const float* __restrict__ max_logits,
+                                 const int* __restrict__ seq_lens, int num_seqs, int num_heads,
+                                 int head_size, int max_partitions) {
+  extern __shared__ float s_w[];  // [warps][max_partitions]
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int item = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (item >= num_seqs * num_heads) return;
+  const int seq = item / num_heads;
+  const int len = seq_lens[seq];
+  const int np = (len + kPartitionTokens - 1) / kPartitionTokens;
+  if (np <= 1) return;
+  float* w = s_w + warp * max_partitions;
+  const float* ml = max_logits + int64_t(item) * max_partitions;
+  const float* es = exp_sums + int64_t(item) * max_partitions;
+  float mx = -INFINITY;
+  for (int j = lane; j < np; j += 32) mx = fmaxf(mx, ml[j]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+  for (int j = lane; j < np; j += 32) {
+    const float v = es[j] * exp2f(ml[j] - mx);
+    w[j] = v;
+    sum += v;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  __syncwarp();
+  const float inv = __fdividef(1.f, sum + 1e-6f);
+  const QT* tp = tmp_out + int64_t(item) * max_partitions * head_size;
+  QT* op = out + int64_t(item) * head_size;
+  for (int d = lane; d < head_size; d += 32) {
+    float acc = 0.f;
+    for (int j = 0; j < np; ++j) acc += to_f32(tp[int64_t(j) * head_size + d]) * w[j];
+    op[d] = from_f32<QT>(acc * inv);
+  }
+}
+
+// ------------------------------------------------------------------ generic decode
+// Fallback for every combination the tensor-core kernel is not built for
+// (fp32 tensors, head size 120, block size 8, unaligned strides, G > 32).
+// One warp per (head, sequence, partition); fp32 math throughout.
+template <typename CT, int KV>
+__device__ __forceinline__ float cache_to_f32(CT v) {
+  if constexpr (KV == kCache16) return to_f32(v);
+  else return fp8_to_f32<KV == kCacheE5M2>(v);
+}
+
+constexpr int kGenericWarps = 4;
+
+template <typename QT, typename CT, int KV>
+__global__ void __launch_bounds__(kGenericWarps * 32)
+pa_generic_kernel(const DecodeParams p, int head_size, int x) {
+  extern __shared__ float s_gen[];  // per warp: q[head_size] + logits[512]
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int per_warp = head_size + kPartitionTokens;
+  float* sq = s_gen + warp * per_warp;
+  float* sl = sq + head_size;
+
+  const int P = p.max_partitions > 0 ? p.max_partitions : 1;
+  const int64_t item = int64_t(blockIdx.x) * kGenericWarps + warp;
+  if (item >= int64_t(p.num_seqs) * p.num_heads * P) return;
+  const int part = int(item % P);
+  const int head = int((item / P) % p.num_heads);
+  const int seq = int(item / (int64_t(P) * p.num_heads));
+  const int len = p.seq_lens[seq];
+  const bool split = p.max_partitions > 0;
+  const int nparts = split ? max(1, (len + kPartitionTokens - 1) / kPartitionTokens) : 1;
+  if (part >= nparts) return;
+  const int t0 = split ? part * kPartitionTokens : 0;
+  const int t1 = split ? min(len, t0 + kPartitionTokens) : len;
+  const int B = p.block_size;
+  const int kvh = head / p.group;
+  const float kq = KV == kCache16 ? 1.f : *p.k_scale;
+  const float vo = KV == kCache16 ? 1.f : *p.v_scale;
+  const float qk_scale = p.scale * kLog2e * kq;
+  const float slope = p.alibi ? p.alibi[head] * kLog2e : 0.f;
+
+  const QT* q = static_cast<const QT*>(p.q) + int64_t(seq) * p.q_stride + int64_t(head) * head_size;
+  for (int d = lane; d < head_size; d += 32) sq[d] = to_f32(q[d]);
+  __syncwarp();
+
+  const CT* kc = static_cast<const CT*>(p.kc);
+  const CT* vc = static_cast<const CT*>(p.vc);
+  const int* bt = p.block_tables + int64_t(seq) * p.max_blocks_per_seq;
+  constexpr int kMaxAcc = 8;  // head_size <= 256
+  float acc[kMaxAcc];
+#pragma unroll
+  for (int i = 0; i < kMaxAcc; ++i) acc[i] = 0.f;
+  float m = -INFINITY, l = 0.f;
+
+  for (int ts = t0; ts < t1; ts += kPartitionTokens) {
+    const int n = min(kPartitionTokens, t1 - ts);
+    float lmax = -INFINITY;
+    for (int i = lane; i < n; i += 32) {
+      const int tok = ts + i;
+      const int64_t blk = bt[tok / B];
+      const int off = tok % B;
+      const CT* kp = kc + blk * p.kv_block_stride + int64_t(kvh) * p.kv_head_stride + off * x;
+      float dot = 0.f;
+      for (int d0 = 0; d0 < head_size; d0 += x) {
+        const CT* kk = kp + int64_t(d0 / x) * B * x;
+        for (int e = 0; e < x; ++e) dot += sq[d0 + e] * cache_to_f32<CT, KV>(kk[e]);
+      }
+      float s = dot * qk_scale;
+      if (p.alibi) s += slope * float(tok - len + 1);
+      sl[i] = s;
+      lmax = fmaxf(lmax, s);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, o));
+    const float m_new = fmaxf(m, lmax);
+    const float alpha = exp2f(m - m_new);
+    float lsum = 0.f;
+    for (int i = lane; i < n; i += 32) {
+      const float pv = exp2f(sl[i] - m_new);
+      sl[i] = pv;
+      lsum += pv;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+    l = l * alpha + lsum;
+    m = m_new;
+#pragma unroll
+    for (int i = 0; i < kMaxAcc; ++i) acc[i] *= alpha;
+    __syncwarp();
+    for (int i = 0; i < n; ++i) {
+      const int tok = ts + i;
+      const int64_t blk = bt[tok / B];
+      const int off = tok % B;
+      const float pv = sl[i];
+      const CT* vp = vc + blk * p.kv_block_stride + int64_t(kvh) * p.kv_head_stride + off;
+#pragma unroll
+      for (int j = 0; j < kMaxAcc; ++j) {
+        const int d = lane + 32 * j;
+        if (d < head_size) acc[j] += pv * cache_to_f32<CT, KV>(vp[int64_t(d) * B]);
+      }
+    }
+    __syncwarp();
+  }
+
+  const float inv = vo * __fdividef(1.f, l + 1e-6f);
+  const bool direct = nparts == 1;
+  QT* o;
+  if (direct) {
+    o = static_cast<QT*>(p.out) + (int64_t(seq) * p.num_heads + head) * head_size;
+  } else {
+    const int64_t idx = (int64_t(seq) * p.num_heads + head) * p.max_partitions + part;
+    o = static_cast<QT*>(p.tmp_out) + idx * head_size;
+    if (lane == 0) {
+      p.max_logits[idx] = m;
+      p.exp_sums[idx] = l;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kMaxAcc; ++j) {
+    const int d = lane + 32 * j;
+    if (d < head_size) o[d] = from_f32<QT>(acc[j] * inv);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+__device__ unsigned g_sched_words[256][2];  // zero-initialised; self-resetting per launch
+
+static unsigned* sched_slot() {
+  constexpr int kMaxDev = 64;
+  static unsigned* base[kMaxDev] = {};
+  static std::atomic<unsigned> rr{0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return nullptr;
+  unsigned* b = __atomic_load_n(&base[dev], __ATOMIC_ACQUIRE);
+  if (b == nullptr) {
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&b), g_sched_words) != cudaSuccess)
+      return nullptr;
+    __atomic_store_n(&base[dev], b, __ATOMIC_RELEASE);
+  }
+  return b + 2 * (rr.fetch_add(1, std::memory_order_relaxed) & 255u);
+}
+
+static int sm_count() {
+  static int cache[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cache[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    cache[dev] = n;
+  }
+  return cache[dev];
+}
+
+static DecodeLaunchFn find_decode(int d, int qdt, int kv, int gp) {
+  switch (d) {
+    case 32: return find_decode_d32(qdt, kv, gp);
+    case 64: return find_decode_d64(qdt, kv, gp);
+    case 80: return find_decode_d80(qdt, kv, gp);
+    case 96: return find_decode_d96(qdt, kv, gp);
+    case 112: return find_decode_d112(qdt, kv, gp);
+    case 128: return find_decode_d128(qdt, kv, gp);
+    case 192: return find_decode_d192(qdt, kv, gp);
+    case 256: return find_decode_d256(qdt, kv, gp);
+  }
+  return nullptr;
+}
+
+template <typename QT>
+static int launch_generic(const DecodeParams& p, const b200pa_attn_args& a, cudaStream_t s) {
+  const int P = p.max_partitions > 0 ? p.max_partitions : 1;
+  const int64_t items = int64_t(p.num_seqs) * p.num_heads * P;
+  const int grid = int((items + kGenericWarps - 1) / kGenericWarps);
+  const size_t smem = size_t(kGenericWarps) * (a.head_size + kPartitionTokens) * sizeof(float);
+  const int x_wide = 16 / int(sizeof(QT));
+  switch (a.kv_dtype) {
+    case B200PA_KV_AUTO:
+      pa_generic_kernel<QT, QT, kCache16><<<grid, kGenericWarps * 32, smem, s>>>(p, a.head_size, x_wide);
+      break;
+    case B200PA_KV_FP8_E4M3:
+      pa_generic_kernel<QT, uint8_t, kCacheE4M3><<<grid, kGenericWarps * 32, smem, s>>>(p, a.head_size, 16);
+      break;
+    case B200PA_KV_FP8_E5M2:
+      pa_generic_kernel<QT, uint8_t, kCacheE5M2><<<grid, kGenericWarps * 32, smem, s>>>(p, a.head_size, 16);
+      break;
+    default:
+      set_error("Unsupported data type of kv cache: %d", a.kv_dtype);
+      return B200PA_EUNSUPPORTED;
+  }
+  count_launch();
+  B200PA_CHECK_CUDA(cudaGetLastError());
+  return B200PA_OK;
+}
+
+template <typename QT>
+static int launch_reduce(const DecodeParams& p, int head_size, cudaStream_t s) {
+  const int warps = 4;
+  const int items = p.num_seqs * p.num_heads;
+  const int grid = (items + warps - 1) / warps;
+  const size_t smem = size_t(warps) * p.max_partitions * sizeof(float);
+  pa_reduce_kernel<QT><<<grid, warps * 32, smem, s>>>(
+      static_cast<QT*>(p.out), static_cast<const QT*>(p.tmp_out), p.exp_sums, p.max_logits,
+      p.seq_lens, p.num_seqs, p.num_heads, head_size, p.max_partitions);
+  count_launch();
+  B200PA_CHECK_CUDA(cudaGetLastError());
+  return B200PA_OK;
+}
+
+// Environment switch for tests: B200PA_FORCE_GENERIC=1 routes everything through
+// the SIMT kernel so the two implementations can be compared on a GPU.
+static bool force_generic() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("B200PA_FORCE_GENERIC");
+    v = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v == 1;
+}
+
+static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
+  B200PA_CHECK_ARG(a != nullptr, "args is NULL");
+  B200PA_CHECK_ARG(a->num_seqs >= 0 && a->num_heads > 0 && a->num_kv_heads > 0 && a->head_size > 0,
+                   "bad sizes: num_seqs=%d num_heads=%d num_kv_heads=%d head_size=%d", a->num_seqs,
+                   a->num_heads, a->num_kv_heads, a->head_size);
+  B200PA_CHECK_ARG(a->num_heads % a->num_kv_heads == 0,
+                   "num_heads %d is not a multiple of num_kv_heads %d", a->num_heads,
+                   a->num_kv_heads);
+  if (a->blocksparse_vert_stride > 1) {
+    set_error("block-sparse paged attention (blocksparse_vert_stride=%d) is not supported",
+              a->blocksparse_vert_stride);
+    return B200PA_EUNSUPPORTED;
+  }
+  // same dispatch tables as the reference launchers (paged_attention_v1.cu:90-158)
+  static const int kHeadSizes[] = {32, 64, 80, 96, 112, 120, 128, 192, 256};
+  bool head_ok = false;
+  for (int hs : kHeadSizes) head_ok |= (hs == a->head_size);
+  if (!head_ok) {
+    set_error("Unsupported head size: %d", a->head_size);
+    return B200PA_EUNSUPPORTED;
+  }
+  if (a->block_size != 8 && a->block_size != 16 && a->block_size != 32) {
+    set_error("Unsupported block size: %d", a->block_size);
+    return B200PA_EUNSUPPORTED;
+  }
+  if (a->q_dtype != B200PA_F32 && a->q_dtype != B200PA_F16 && a->q_dtype != B200PA_BF16) {
+    set_error("Unsupported input type of kv cache: %d", a->q_dtype);
+    return B200PA_EUNSUPPORTED;
+  }
+  if (a->kv_dtype != B200PA_KV_AUTO && a->kv_dtype != B200PA_KV_FP8_E4M3 &&
+      a->kv_dtype != B200PA_KV_FP8_E5M2) {
+    set_error("Unsupported data type of kv cache: %d", a->kv_dtype);
+    return B200PA_EUNSUPPORTED;
+  }
+  if (a->num_seqs == 0) return B200PA_OK;
+  B200PA_CHECK_ARG(a->out && a->query && a->key_cache && a->value_cache && a->block_tables &&
+                       a->seq_lens,
+                   "null tensor pointer");
+  B200PA_CHECK_ARG(a->kv_dtype == B200PA_KV_AUTO || (a->k_scale && a->v_scale),
+                   "fp8 kv cache needs k_scale and v_scale");
+  B200PA_CHECK_ARG(a->max_num_blocks_per_seq > 0, "max_num_blocks_per_seq must be positive");
+  if (v2) {
+    B200PA_CHECK_ARG(a->exp_sums && a->max_logits && a->tmp_out, "v2 needs exp_sums/max_logits/tmp_out");
+    B200PA_CHECK_ARG(a->max_num_partitions >= 1 &&
+                         int64_t(a->max_num_partitions) * kPartitionTokens >= a->max_seq_len,
+                     "max_num_partitions=%d does not cover max_seq_len=%d", a->max_num_partitions,
+                     a->max_seq_len);
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  DecodeParams p{};
+  p.out = a->out;
+  p.q = a->query;
+  p.kc = a->key_cache;
+  p.vc = a->value_cache;
+  p.block_tables = a->block_tables;
+  p.seq_lens = a->seq_lens;
+  p.alibi = a->alibi_slopes;
+  p.k_scale = a->k_scale;
+  p.v_scale = a->v_scale;
+  p.exp_sums = a->exp_sums;
+  p.max_logits = a->max_logits;
+  p.tmp_out = a->tmp_out;
+  p.q_stride = a->q_stride;
+  p.kv_block_stride = a->kv_block_stride;
+  p.kv_head_stride = a->kv_head_stride;
+  p.num_seqs = a->num_seqs;
+  p.num_heads = a->num_heads;
+  p.num_kv_heads = a->num_kv_heads;
+  p.block_size = a->block_size;
+  p.max_blocks_per_seq = a->max_num_blocks_per_seq;
+  // a single partition needs no scratch and no reduce: run it unsplit
+  const bool split = v2 && a->max_num_partitions > 1;
+  p.max_partitions = split ? a->max_num_partitions : 0;
+  p.group = a->num_heads / a->num_kv_heads;
+  p.scale = a->scale;
+
+  // ---- can the tensor-core kernel take it?
+  const int es = a->kv_dtype == B200PA_KV_AUTO ? 2 : 1;
+  auto aligned = [](const void* ptr, uintptr_t n) { return reinterpret_cast<uintptr_t>(ptr) % n == 0; };
+  const int gp = p.group <= 8 ? 1 : 2;
+  DecodeLaunchFn fn = nullptr;
+  bool fast = !force_generic() && a->q_dtype != B200PA_F32 &&
+              (a->block_size == 16 || a->block_size == 32) && a->head_size % 16 == 0 &&
+              aligned(a->key_cache, 16) && aligned(a->value_cache, 16) && aligned(a->query, 16) &&
+              aligned(a->out, 16) && (!split || aligned(a->tmp_out, 16)) &&
+              (a->kv_block_stride * es) % 16 == 0 && (a->kv_head_stride * es) % 16 == 0 &&
+              a->q_stride % 8 == 0;
+  if (fast) fn = find_decode(a->head_size, a->q_dtype, a->kv_dtype, gp);
+  int rc;
+  if (fn != nullptr) {
+    p.head_groups = (p.group + 8 * gp - 1) / (8 * gp);
+    const size_t stage_bytes = size_t(2) * a->head_size * a->block_size * es;
+    // The partition prefix table lives in shared memory; very large batches run
+    // without it (one work item per sequence and kv head).
+    p.use_table = split ? 1 : 0;
+    size_t table_bytes = p.use_table ? size_t((p.num_seqs + 1 + 3) & ~3) * 4 : 0;
+    const size_t budget_total = 227 * 1024 - 1024;  // static smem + slack
+    if (table_bytes > 48 * 1024) {
+      set_error("num_seqs=%d is too large for the split-KV partition table", a->num_seqs);
+      return B200PA_EUNSUPPORTED;
+    }
+    const size_t budget = budget_total - table_bytes - 1024 /* mbarriers */;
+    int nwarps = int(std::min<size_t>(kMaxWarps, budget / (3 * stage_bytes)));
+    if (nwarps < 1) nwarps = 1;
+    int ns = int(std::min<size_t>(8, budget / (size_t(nwarps) * stage_bytes)));
+    if (ns < 2) {
+      set_error("head_size=%d block_size=%d does not fit the shared-memory pipeline", a->head_size,
+                a->block_size);
+      return B200PA_EUNSUPPORTED;
+    }
+    p.nstages = ns;
+    p.sched = sched_slot();
+    p.status = device_status_ptr();
+    if (p.sched == nullptr || p.status == nullptr) {
+      set_error("could not resolve device-side scheduler/status words");
+      return B200PA_ECUDA;
+    }
+    const size_t bars_bytes = (size_t(nwarps) * ns * 8 + 127) & ~size_t(127);
+    const size_t smem = table_bytes + bars_bytes + size_t(nwarps) * ns * stage_bytes;
+    const int grid = sm_count();
+    cudaError_t e = fn(p, grid, nwarps * 32, smem, s);
+    count_launch();
+    if (e != cudaSuccess) {
+      set_error("decode kernel launch failed: %s", cudaGetErrorString(e));
+      return B200PA_ECUDA;
+    }
+    rc = B200PA_OK;
+  } else {
+    if (a->head_size > 256) {
+      set_error("Unsupported head size: %d", a->head_size);
+      return B200PA_EUNSUPPORTED;
+    }
+    switch (a->q_dtype) {
+      case B200PA_F32: rc = launch_generic<float>(p, *a, s); break;
+      case B200PA_F16: rc = launch_generic<__half>(p, *a, s); break;
+      default: rc = launch_generic<__nv_bfloat16>(p, *a, s); break;
+    }
+  }
+  if (rc != B200PA_OK) return rc;
+  if (split) {
+    switch (a->q_dtype) {
+      case B200PA_F32: return launch_reduce<float>(p, a->head_size, s);
+      case B200PA_F16: return launch_reduce<__half>(p, a->head_size, s);
+      default: return launch_reduce<__nv_bfloat16>(p, a->head_size, s);
+    }
+  }
+  return B200PA_OK;
+}
+
+}  // namespace b200pa
+
+extern "C" int b200pa_paged_attention_v1(const b200pa_attn_args* args, void* stream) {
+  return b200pa::attention_entry(args, stream, false);
+}
+
+extern "C" int b200pa_paged_attention_v2(const b200pa_attn_args* args, void* stream) {
+  return b200pa::attention_entry(args, stream, true);
+}
