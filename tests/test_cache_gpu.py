@@ -1,0 +1,144 @@
+"""GPU parity of reshape_and_cache / reshape_and_cache_flash / convert_fp8:
+bit-exact against the CPU oracle and the reference's CUDA kernels.  Case matrix
+modelled on tests/kernels/attention/test_cache.py:129-410 of the reference."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import paged_oracle as O
+from vllm_b200 import _custom_ops as ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _slots(rng, T, total, runs=True):
+    s = rng.permutation(total)[:T].astype(np.int64)
+    if runs and T >= 40:
+        # a few runs of consecutive slots (whole blocks and ragged pieces)
+        base = (total // 2 // 32) * 32
+        run = np.arange(base, base + 37, dtype=np.int64)
+        rest = np.setdiff1d(rng.permutation(total), run)[:T - 37]
+        s = np.concatenate([rest[:3], run, rest[3:]])
+    s[1] = -1
+    return s
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("kv", ["auto", "fp8", "fp8_e5m2"])
+@pytest.mark.parametrize("head_size", [64, 80, 256])
+@pytest.mark.parametrize("block_size", [8, 16, 32])
+def test_reshape_and_cache_bit_exact(dtype, kv, head_size, block_size, ref_cuda_ops):
+    if kv != "auto" and head_size % 16:
+        pytest.skip("fp8 caches need head_size % 16 == 0")
+    T, H, NB = 123, 8, 96
+    rng = np.random.default_rng(0)
+    g = torch.Generator(device=DEV).manual_seed(0)
+    key = torch.randn(T, H, head_size, device=DEV, generator=g).mul(3).to(dtype)
+    val = torch.randn(T, H, head_size, device=DEV, generator=g).mul(3).to(dtype)
+    key[0, 0, 0] = float("nan")
+    val[2, 1, 3] = float("inf")
+    slots = torch.from_numpy(_slots(rng, T, NB * block_size)).to(DEV)
+    fp8 = kv != "auto"
+    cdt = torch.uint8 if fp8 else dtype
+    x = 16 // (1 if fp8 else key.element_size())
+    ks = (key.float().nan_to_num(0, 0, 0).abs().amax() / 64.0).reshape(())
+    vs = (val.float().nan_to_num(0, 0, 0).abs().amax() / 64.0).reshape(())
+    kc = torch.zeros(NB, H, head_size // x, block_size, x, dtype=cdt, device=DEV)
+    vc = torch.zeros(NB, H, head_size, block_size, dtype=cdt, device=DEV)
+    ops.reshape_and_cache(key, val, kc, vc, slots, kv, ks, vs)
+    kco, vco = torch.zeros_like(kc, device="cpu"), torch.zeros_like(vc, device="cpu")
+    O.reshape_and_cache(key.cpu(), val.cpu(), kco, vco, slots.cpu(), kv, float(ks), float(vs))
+    same = lambda a, b: torch.equal(a.cpu().view(torch.uint8), b.cpu().view(torch.uint8))
+    assert same(kc, kco) and same(vc, vco)
+    if ref_cuda_ops is not None:
+        kcr, vcr = torch.zeros_like(kc), torch.zeros_like(vc)
+        ref_cuda_ops[1].reshape_and_cache(key, val, kcr, vcr, slots, kv, ks, vs)
+        assert same(kc, kcr) and same(vc, vcr)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("kv", ["auto", "fp8"])
+@pytest.mark.parametrize("layout", ["NHD", "HND"])
+@pytest.mark.parametrize("head_size", [64, 80, 256])
+@pytest.mark.parametrize("block_size", [8, 16, 32])
+def test_reshape_and_cache_flash_bit_exact(dtype, kv, layout, head_size, block_size, ref_cuda_ops):
+    T, H, NB = 77, 8, 64
+    rng = np.random.default_rng(1)
+    g = torch.Generator(device=DEV).manual_seed(1)
+    # key has more rows than slot_mapping (padding for CUDA graphs) and a padded row stride
+    pad = torch.randn(T + 5, H * head_size + 16, device=DEV, generator=g).to(dtype)
+    key = pad[:, :H * head_size].view(T + 5, H, head_size)
+    val = torch.randn(T + 5, H, head_size, device=DEV, generator=g).to(dtype)
+    slots = torch.from_numpy(_slots(rng, T, NB * block_size, runs=False)).to(DEV)
+    fp8 = kv != "auto"
+    cdt = torch.uint8 if fp8 else dtype
+    ks = torch.tensor(0.037, device=DEV)
+    vs = torch.tensor(0.051, device=DEV)
+
+    def mk():
+        if layout == "NHD":
+            a = torch.zeros(NB, block_size, H, head_size, dtype=cdt, device=DEV)
+            b = torch.zeros_like(a)
+            return a, b
+        a = torch.zeros(NB, H, block_size, head_size, dtype=cdt, device=DEV)
+        b = torch.zeros_like(a)
+        return a.permute(0, 2, 1, 3), b.permute(0, 2, 1, 3)
+
+    kc, vc = mk()
+    ops.reshape_and_cache_flash(key, val, kc, vc, slots, kv, ks, vs)
+    kco, vco = torch.zeros(kc.shape, dtype=cdt), torch.zeros(vc.shape, dtype=cdt)
+    O.reshape_and_cache_flash(key.cpu(), val.cpu(), kco, vco, slots.cpu(), kv, float(ks), float(vs))
+    same = lambda a, b: torch.equal(a.cpu().contiguous().view(torch.uint8), b.cpu().contiguous().view(torch.uint8))
+    assert same(kc, kco) and same(vc, vco)
+    if ref_cuda_ops is not None:
+        kcr, vcr = mk()
+        ref_cuda_ops[1].reshape_and_cache_flash(key, val, kcr, vcr, slots, kv, ks, vs)
+        assert same(kc, kcr) and same(vc, vcr)
+
+
+def test_fp8_quantiser_exhaustive_on_device(ref_cuda_ops):
+    """Every bf16 bit pattern through the device quantiser == oracle == reference."""
+    bits = torch.arange(65536, dtype=torch.int32).to(torch.int16)
+    x = bits.view(torch.bfloat16).to(DEV)
+    for kv in ("fp8", "fp8_e5m2"):
+        for scale in (1.0, 0.011826, 3.7):
+            dst = torch.empty(65536, dtype=torch.uint8, device=DEV)
+            ops.convert_fp8(dst, x, scale, kv)
+            want = O.quantize_fp8(x.cpu(), scale, kv)
+            assert torch.equal(dst.cpu(), want), (kv, scale)
+            if ref_cuda_ops is not None and kv == "fp8":
+                r = torch.empty_like(dst)
+                ref_cuda_ops[1].convert_fp8(r.view(1, -1), x.view(1, -1), scale, kv)
+                assert torch.equal(r, dst)
+
+
+def test_convert_fp8_round_trip():
+    """reference tests/kernels/attention/test_cache.py:514-545"""
+    g = torch.Generator(device=DEV).manual_seed(2)
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        x = torch.empty(4, 1024, device=DEV).uniform_(-224, 224, generator=g).to(dtype)
+        q = torch.empty_like(x, dtype=torch.uint8)
+        ops.convert_fp8(q, x)
+        y = torch.empty_like(x)
+        ops.convert_fp8(y, q)
+        torch.testing.assert_close(x, y, atol=1e-3, rtol=0.25)
+        want = O.dequantize_fp8(q.cpu(), 1.0, dtype)
+        assert torch.equal(y.cpu(), want)
+
+
+def test_write_then_attend_uses_the_written_tokens():
+    """reshape_and_cache -> paged_attention_v2 on the same cache (the decode step)."""
+    from vllm_b200 import workloads as W
+    w = W.config3(DEV, num_seqs=4, seq_len=1024, new_tokens=128)
+    ops.reshape_and_cache(w.new_key, w.new_value, w.key_cache, w.value_cache, w.slot_mapping, "fp8",
+                          w.k_scale, w.v_scale)
+    kc, vc = w.key_cache.cpu().clone(), w.value_cache.cpu().clone()
+    out = W.run_attention(w, version="v2").cpu()
+    want = O.paged_attention(w.query.cpu(), kc, vc, w.num_kv_heads, w.scale, w.block_tables.cpu(),
+                             w.seq_lens.cpu(), None, "fp8", float(w.k_scale), float(w.v_scale), mode="f64")
+    torch.testing.assert_close(out.double(), want, atol=2e-2, rtol=2e-2)
+    # the last 128 positions of sequence 0 hold exactly the quantised new tokens
+    k0, _ = O.gather_kv(kc, vc, w.block_tables.cpu()[0], 1024, "fp8", 1.0, 1.0, torch.float32)
+    qk = O.quantize_fp8(w.new_key[:128].cpu(), float(w.k_scale), "fp8").view(torch.float8_e4m3fn).float()
+    assert torch.equal(k0[-128:], qk)
