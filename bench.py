@@ -112,9 +112,16 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def build_workload(name: str, device, world: int, rank: int):
+def build_workload(name: str, device, world: int, rank: int, num_seqs=None):
     from vllm_b200 import workloads as W
 
+    if num_seqs is not None:
+        if name == "cfg2":
+            return W.config2(device, seed=0, rank=rank, num_seqs=num_seqs), "v2", "weak"
+        if name == "cfg3":
+            return W.config3(device, seed=rank, num_seqs=num_seqs), "v2", "weak"
+        if name == "cfg5":
+            return W.config5(device, world_size=world, rank=rank, num_seqs=num_seqs), "v2", "strong"
     if name == "cfg2":
         return W.config2(device, seed=0, rank=rank), "v2", "weak"
     if name == "cfg1":
@@ -185,11 +192,13 @@ def cpu_reference_leg(w, steps: int, warmup: int, budget_s: float = 30.0, min_s:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--num-seqs", type=int, default=None,
+                    help="override the batch size of cfg2/cfg3/cfg5 (small cases for profiler captures)")
     a = ap.parse_args()
     a.warmup = max(3, a.warmup)
 
@@ -206,7 +215,7 @@ def main() -> int:
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
 
-    w, version, scaling = build_workload(a.workload, dev, world, rank)
+    w, version, scaling = build_workload(a.workload, dev, world, rank, a.num_seqs)
     cfg = {
         "workload": f"{w.name}: paged_attention_{version}, num_seqs={w.num_seqs} per GPU, "
                     f"{w.num_heads} query / {w.num_kv_heads} KV heads, head_size={w.head_size}, "
