@@ -275,3 +275,44 @@ def run_attention(w: Workload, out: torch.Tensor | None = None, version: str = "
                                w.block_size, w.max_seq_len, w.alibi_slopes, w.kv_cache_dtype,
                                w.k_scale, w.v_scale)
     return out
+
+
+def shard_kv_heads(w: Workload, world_size: int, rank: int) -> Workload:
+    """Rank `rank`'s share of `w` when KV heads are partitioned: `Hkv/world_size` kv heads of
+    every block and the query heads that map to them (kv_head = head // G); block tables and
+    seq_lens are replicated.  The slices are copies, so each rank holds only its own shard."""
+    assert w.num_kv_heads % world_size == 0
+    hk = w.num_kv_heads // world_size
+    g = w.num_heads // w.num_kv_heads
+    ks, qs = slice(rank * hk, (rank + 1) * hk), slice(rank * hk * g, (rank + 1) * hk * g)
+    return dataclasses.replace(
+        w, name=f"{w.name}/kvheads{rank}of{world_size}", query=w.query[:, qs].contiguous(),
+        key_cache=w.key_cache[:, ks].contiguous(), value_cache=w.value_cache[:, ks].contiguous(),
+        num_kv_heads=hk,
+        alibi_slopes=None if w.alibi_slopes is None else w.alibi_slopes[qs].contiguous())
+
+
+def shard_sequences(w: Workload, world_size: int, rank: int) -> Workload:
+    """Rank `rank`'s share of `w` when sequences are partitioned: `S/world_size` sequences with a
+    private block pool holding only their blocks, block ids renumbered locally."""
+    assert w.num_seqs % world_size == 0
+    per = w.num_seqs // world_size
+    ss = slice(rank * per, (rank + 1) * per)
+    lens = w.seq_lens[ss].cpu().numpy().astype(np.int64)
+    need = np.ceil(lens / w.block_size).astype(np.int64)
+    bt = w.block_tables[ss].cpu().numpy()
+    used = np.concatenate([bt[s, :need[s]] for s in range(per)]) if per else np.zeros(0, np.int64)
+    uniq, inv = np.unique(used, return_inverse=True)
+    if uniq.size == 0:
+        uniq = np.zeros(1, dtype=np.int64)
+    local = np.zeros_like(bt)
+    off = 0
+    for s in range(per):
+        local[s, :need[s]] = inv[off:off + need[s]]
+        off += need[s]
+    idx = torch.from_numpy(uniq.astype(np.int64)).to(w.key_cache.device)
+    return dataclasses.replace(
+        w, name=f"{w.name}/seqs{rank}of{world_size}", query=w.query[ss].contiguous(),
+        key_cache=w.key_cache[idx].contiguous(), value_cache=w.value_cache[idx].contiguous(),
+        block_tables=torch.from_numpy(local).to(w.block_tables.device),
+        seq_lens=w.seq_lens[ss].contiguous())
