@@ -17,9 +17,9 @@
  *   - Every function returns 0 on success or a negative B200PA_E* code; it never
  *     throws and never aborts.  b200pa_last_error() returns a thread-local,
  *     human-readable message for the last non-zero return on this thread.
- *   - Like the reference ops, the launchers do not synchronise, do not allocate
- *     device memory and do not read device data on the host, so they may be
- *     recorded into a CUDA graph.
+ *   - Like the reference ops they replace, the launchers do not synchronise, do
+ *     not allocate device memory and do not read device data on the host, so
+ *     those ops may be recorded into a CUDA graph as the reference's are.
  *   - No bounds checks on block-table or slot indices (same contract as the
  *     reference kernels, csrc/attention/attention_kernels.cuh:252-253).
  *   - All strides are in ELEMENTS of the tensor they describe.
@@ -133,6 +133,33 @@ int b200pa_paged_attention_v1(const b200pa_attn_args* args, void* stream);
  * (csrc/attention/paged_attention_v2.cu:167-192, attention_kernels.cuh:559-664):
  * split-KV over 512-token partitions using the caller's scratch. */
 int b200pa_paged_attention_v2(const b200pa_attn_args* args, void* stream);
+
+/*
+ * paged_attention_v2 for callers that cannot hand over scratch memory.  It has no
+ * counterpart in the reference, whose caller always allocates exp_sums,
+ * max_logits and tmp_out (vllm/attention/ops/paged_attn.py:164-174).
+ *
+ * Who needs it: a host that binds this C ABI directly and owns no device
+ * allocator, and serving processes that gave all free HBM to the KV-cache pool
+ * at start-up, where a later cudaMalloc can fail.  This entry point allocates
+ * nothing (no cudaMalloc / cudaFree, no allocating library call): the split-KV
+ * scratch is a 32 MiB array built into the library, resident on every GPU that
+ * loads it until the process exits.
+ *
+ *   - args->exp_sums, max_logits, tmp_out and max_num_partitions are ignored
+ *     (may be NULL / 0); everything else is as for b200pa_paged_attention_v2.
+ *   - Limit: num_seqs * num_heads * ceil(max_seq_len/512) * (8 + head_size *
+ *     sizeof(query element)) bytes, each of the three regions rounded up to
+ *     256 bytes, must fit 32 MiB; larger problems return B200PA_EINVAL with a
+ *     message and launch nothing.
+ *   - The first call on a device resolves the array's device address; make that
+ *     call before any stream capture.
+ *   - All calls on one device share the array.  Calls that may overlap on the
+ *     GPU (different streams without an ordering between them) race on it; keep
+ *     them on one stream or order them with events.  Nothing in the array has
+ *     to be cleared between calls.
+ */
+int b200pa_paged_attention_v2_noalloc(const b200pa_attn_args* args, void* stream);
 
 /*
  * Arguments of reshape_and_cache / reshape_and_cache_flash.

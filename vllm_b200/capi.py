@@ -20,6 +20,7 @@ EXPORTS = (
     "b200pa_kv_dtype_from_string",
     "b200pa_paged_attention_v1",
     "b200pa_paged_attention_v2",
+    "b200pa_paged_attention_v2_noalloc",
     "b200pa_reshape_and_cache",
     "b200pa_reshape_and_cache_flash",
     "b200pa_convert_fp8",
@@ -76,7 +77,8 @@ def lib() -> C.CDLL:
         l.b200pa_kv_dtype_from_string.argtypes = [C.c_char_p]
         l.b200pa_launch_count.restype = C.c_int64
         l.b200pa_launch_count.argtypes = [C.c_int]
-        for name in ("b200pa_paged_attention_v1", "b200pa_paged_attention_v2"):
+        for name in ("b200pa_paged_attention_v1", "b200pa_paged_attention_v2",
+                     "b200pa_paged_attention_v2_noalloc"):
             getattr(l, name).argtypes = [C.POINTER(AttnArgs), C.c_void_p]
         for name in ("b200pa_reshape_and_cache", "b200pa_reshape_and_cache_flash"):
             getattr(l, name).argtypes = [C.POINTER(CacheArgs), C.c_void_p]
@@ -106,6 +108,11 @@ def paged_attention_v1(args: AttnArgs, stream: int = 0) -> None:
 
 def paged_attention_v2(args: AttnArgs, stream: int = 0) -> None:
     check(lib().b200pa_paged_attention_v2(C.byref(args), C.c_void_p(stream)))
+
+
+def paged_attention_v2_noalloc(args: AttnArgs, stream: int = 0) -> None:
+    """v2 with the library's built-in 32 MiB split-KV scratch (allocates nothing; see b200pa.h)."""
+    check(lib().b200pa_paged_attention_v2_noalloc(C.byref(args), C.c_void_p(stream)))
 
 
 def reshape_and_cache(args: CacheArgs, stream: int = 0) -> None:

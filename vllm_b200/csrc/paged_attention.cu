@@ -437,3 +437,75 @@ extern "C" int b200pa_paged_attention_v1(const b200pa_attn_args* args, void* str
 extern "C" int b200pa_paged_attention_v2(const b200pa_attn_args* args, void* stream) {
   return b200pa::attention_entry(args, stream, true);
 }
+
+// ------------------------------------------------------------------ v2 without caller scratch
+// Split-KV scratch (exp_sums, max_logits, tmp_out) for callers that cannot
+// provide device memory of their own: a plain C host that binds this library
+// has no allocator to ask, and a serving process that has already handed all
+// free HBM to its KV-cache pool can see cudaMalloc fail late.  The buffer is a
+// file-scope device array: every GPU that loads the library holds these 32 MiB
+// until the process exits.  All calls on a device share it and it keeps the
+// previous call's contents; nothing in it has to start at zero, because the
+// decode kernel writes every partial (m, l, O) that the reduce kernel reads.
+namespace b200pa {
+
+constexpr size_t kBuiltinScratchBytes = size_t(32) << 20;
+static __device__ __align__(256) unsigned char g_builtin_scratch[kBuiltinScratchBytes];
+
+// `g_builtin_scratch` names a host-side stand-in in host code, not a device
+// address: resolve the device address once per device, with that device current.
+static unsigned char* builtin_scratch_ptr() {
+  constexpr int kMaxDev = 64;
+  static unsigned char* cache[kMaxDev] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDev) {
+    set_error("cudaGetDevice failed or device index out of range");
+    return nullptr;
+  }
+  unsigned char* p = __atomic_load_n(&cache[dev], __ATOMIC_ACQUIRE);
+  if (p == nullptr) {
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_builtin_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      (void)cudaGetLastError();
+      set_error("cudaGetSymbolAddress(built-in scratch) failed: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    __atomic_store_n(&cache[dev], p, __ATOMIC_RELEASE);
+  }
+  return p;
+}
+
+}  // namespace b200pa
+
+extern "C" int b200pa_paged_attention_v2_noalloc(const b200pa_attn_args* args, void* stream) {
+  using namespace b200pa;
+  B200PA_CHECK_ARG(args != nullptr, "args is NULL");
+  B200PA_CHECK_ARG(args->num_seqs >= 0 && args->num_heads > 0 && args->head_size > 0 &&
+                       args->max_seq_len >= 0,
+                   "bad sizes: num_seqs=%d num_heads=%d head_size=%d max_seq_len=%d", args->num_seqs,
+                   args->num_heads, args->head_size, args->max_seq_len);
+  const int64_t parts = std::max<int64_t>(
+      1, (int64_t(args->max_seq_len) + kPartitionTokens - 1) / kPartitionTokens);
+  const int64_t n = int64_t(args->num_seqs) * args->num_heads * parts;
+  const int64_t esize = args->q_dtype == B200PA_F32 ? 4 : 2;
+  auto up = [](int64_t v) { return (v + 255) & ~int64_t(255); };
+  const int64_t stat_bytes = up(n * 4);
+  const int64_t need = 2 * stat_bytes + up(n * args->head_size * esize);
+  if (need > int64_t(kBuiltinScratchBytes)) {
+    set_error("paged_attention_v2_noalloc: num_seqs=%d x num_heads=%d x %lld partitions needs %lld "
+              "bytes of split-KV scratch, the built-in buffer holds %lld; use "
+              "b200pa_paged_attention_v2 with caller scratch",
+              args->num_seqs, args->num_heads, (long long)parts, (long long)need,
+              (long long)kBuiltinScratchBytes);
+    return B200PA_EINVAL;
+  }
+  unsigned char* base = builtin_scratch_ptr();
+  if (base == nullptr) return B200PA_ECUDA;
+  b200pa_attn_args a = *args;
+  a.exp_sums = reinterpret_cast<float*>(base);
+  a.max_logits = reinterpret_cast<float*>(base + stat_bytes);
+  a.tmp_out = base + 2 * stat_bytes;
+  a.max_num_partitions = static_cast<int32_t>(parts);
+  return attention_entry(&a, stream, true);
+}
