@@ -6,7 +6,6 @@
 namespace b200pa {
 
 constexpr int kPartitionTokens = 512;  // split-KV partition, same as the reference's PARTITION_SIZE
-constexpr int kMaxWarps = 8;
 constexpr float kLog2e = 1.4426950408889634f;
 
 // Status codes written to the device status word.
@@ -26,6 +25,7 @@ struct DecodeParams {
   float* max_logits;  // [S, Hq, P]  (m per partition, log2 domain)
   void* tmp_out;      // [S, Hq, P, D] query dtype, normalised partials
   unsigned* sched;    // [0] work ticket, [1] CTAs done (self-resetting)
+  unsigned* arrive;   // per (seq, kv head, head group) count of delivered partials, or nullptr
   int* status;
   int64_t q_stride;
   int64_t kv_block_stride;
@@ -151,6 +151,51 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+
+// Four fp8 bytes -> two packed f16x2 (lo = bytes 0,1; hi = bytes 2,3).
+//
+// kAlu = false: cvt.rn.f16x2.e4m3x2 (exact values).  That instruction issues on the
+//   narrow XU pipe, which saturates near HBM rate when every K and V byte goes through it.
+// kAlu = true: integer ALU ops only.  e4m3 codes are placed into the f16 bit pattern
+//   without re-biasing the exponent, so they come out as value * 2^-8 (exact,
+//   subnormals included) and the caller folds 2^8 into its scale; e4m3 NaN codes
+//   (0x7F / 0xFF) decode as +-480 * 2^-8 rather than NaN.  e5m2 is the upper byte of
+//   an f16, so it comes out unscaled.
+// The decode kernel sends K through one pipe and V through the other.
+template <bool kE5M2, bool kAlu>
+struct Fp8Unpack {
+  static constexpr float kPrescale = (kAlu && !kE5M2) ? 256.f : 1.f;
+};
+
+template <bool kE5M2, bool kAlu>
+__device__ __forceinline__ void fp8x4_to_f16(uint32_t x, uint32_t& lo, uint32_t& hi) {
+  if constexpr (!kAlu) {
+    uint16_t l16, h16;
+    asm("mov.b32 {%0, %1}, %2;" : "=h"(l16), "=h"(h16) : "r"(x));
+    if constexpr (kE5M2) {
+      asm("cvt.rn.f16x2.e5m2x2 %0, %1;" : "=r"(lo) : "h"(l16));
+      asm("cvt.rn.f16x2.e5m2x2 %0, %1;" : "=r"(hi) : "h"(h16));
+    } else {
+      asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(lo) : "h"(l16));
+      asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(hi) : "h"(h16));
+    }
+  } else if constexpr (kE5M2) {
+    lo = prmt(x, 0u, 0x1404u);
+    hi = prmt(x, 0u, 0x3424u);
+  } else {
+    const uint32_t t = (x >> 1) & 0x3F3F3F3Fu;          // exponent + top mantissa bits
+    const uint32_t hb = (x & 0x80808080u) | t;           // high byte of each f16: s0eeeemm
+    const uint32_t lb = (x << 7) & 0x80808080u;          // low byte of each f16: m0000000
+    lo = prmt(lb, hb, 0x5140u);
+    hi = prmt(lb, hb, 0x7362u);
+  }
 }
 
 template <bool kBf16>

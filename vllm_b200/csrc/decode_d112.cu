@@ -2,7 +2,7 @@
 #include "decode_inst.cuh"
 
 namespace b200pa {
-DecodeLaunchFn find_decode_d112(int q_dtype, int kv_dtype, int gp) {
+DecodeKernelInfo find_decode_d112(int q_dtype, int kv_dtype, int gp) {
   return find_decode_for<112>(q_dtype, kv_dtype, gp);
 }
 }  // namespace b200pa

@@ -9,10 +9,23 @@ namespace b200pa {
 using DecodeLaunchFn = cudaError_t (*)(const DecodeParams&, int grid, int threads, size_t smem,
                                        cudaStream_t stream);
 
-template <typename QT, int KV, int D, int GP>
+// A built kernel variant: its launcher and the most warps per CTA it may be launched with.
+struct DecodeKernelInfo {
+  DecodeLaunchFn fn;
+  int max_warps;
+};
+
+// Warps per CTA the kernel is compiled for: 16 when the register budget allows
+// (<= 128 registers per thread), else 8.
+template <int KV, int D, int GP>
+constexpr int decode_max_warps() {
+  return (D * GP <= 128) ? 16 : 8;
+}
+
+template <typename QT, int KV, int D, int GP, int CVT = 2>
 cudaError_t decode_launch(const DecodeParams& p, int grid, int threads, size_t smem,
                           cudaStream_t stream) {
-  auto kern = pa_decode_kernel<QT, KV, D, GP>;
+  auto kern = pa_decode_kernel<QT, KV, D, GP, decode_max_warps<KV, D, GP>(), CVT>;
   // opt in to large dynamic shared memory once per device
   static bool done[64] = {};
   int dev = 0;
@@ -35,33 +48,38 @@ cudaError_t decode_launch(const DecodeParams& p, int grid, int threads, size_t s
   return cudaGetLastError();
 }
 
+template <typename QT, int KV, int D>
+DecodeKernelInfo pick_gp(int gp) {
+  if (gp == 1) return {decode_launch<QT, KV, D, 1>, decode_max_warps<KV, D, 1>()};
+  return {decode_launch<QT, KV, D, 2>, decode_max_warps<KV, D, 2>()};
+}
+
+template <typename QT, int D>
+DecodeKernelInfo pick_kv(int kv_dtype, int gp) {
+  switch (kv_dtype) {
+    case B200PA_KV_AUTO: return pick_gp<QT, kCache16, D>(gp);
+    case B200PA_KV_FP8_E4M3: return pick_gp<QT, kCacheE4M3, D>(gp);
+    case B200PA_KV_FP8_E5M2: return pick_gp<QT, kCacheE5M2, D>(gp);
+  }
+  return {nullptr, 0};
+}
+
 template <int D>
-DecodeLaunchFn find_decode_for(int q_dtype, int kv_dtype, int gp) {
-#define B200PA_PICK(QT)                                                                  \
-  switch (kv_dtype) {                                                                    \
-    case B200PA_KV_AUTO:                                                                 \
-      return gp == 1 ? decode_launch<QT, kCache16, D, 1> : decode_launch<QT, kCache16, D, 2>; \
-    case B200PA_KV_FP8_E4M3:                                                             \
-      return gp == 1 ? decode_launch<QT, kCacheE4M3, D, 1> : decode_launch<QT, kCacheE4M3, D, 2>; \
-    case B200PA_KV_FP8_E5M2:                                                             \
-      return gp == 1 ? decode_launch<QT, kCacheE5M2, D, 1> : decode_launch<QT, kCacheE5M2, D, 2>; \
-  }                                                                                      \
-  return nullptr;
-  if (gp != 1 && gp != 2) return nullptr;
-  if (q_dtype == B200PA_BF16) { B200PA_PICK(__nv_bfloat16) }
-  if (q_dtype == B200PA_F16) { B200PA_PICK(__half) }
-#undef B200PA_PICK
-  return nullptr;
+DecodeKernelInfo find_decode_for(int q_dtype, int kv_dtype, int gp) {
+  if (gp != 1 && gp != 2) return {nullptr, 0};
+  if (q_dtype == B200PA_BF16) return pick_kv<__nv_bfloat16, D>(kv_dtype, gp);
+  if (q_dtype == B200PA_F16) return pick_kv<__half, D>(kv_dtype, gp);
+  return {nullptr, 0};
 }
 
 // One finder per translation unit (defined in decode_d*.cu).
-DecodeLaunchFn find_decode_d32(int q_dtype, int kv_dtype, int gp);
-DecodeLaunchFn find_decode_d64(int q_dtype, int kv_dtype, int gp);
-DecodeLaunchFn find_decode_d80(int q_dtype, int kv_dtype, int gp);
-DecodeLaunchFn find_decode_d96(int q_dtype, int kv_dtype, int gp);
-DecodeLaunchFn find_decode_d112(int q_dtype, int kv_dtype, int gp);
-DecodeLaunchFn find_decode_d128(int q_dtype, int kv_dtype, int gp);
-DecodeLaunchFn find_decode_d192(int q_dtype, int kv_dtype, int gp);
-DecodeLaunchFn find_decode_d256(int q_dtype, int kv_dtype, int gp);
+DecodeKernelInfo find_decode_d32(int q_dtype, int kv_dtype, int gp);
+DecodeKernelInfo find_decode_d64(int q_dtype, int kv_dtype, int gp);
+DecodeKernelInfo find_decode_d80(int q_dtype, int kv_dtype, int gp);
+DecodeKernelInfo find_decode_d96(int q_dtype, int kv_dtype, int gp);
+DecodeKernelInfo find_decode_d112(int q_dtype, int kv_dtype, int gp);
+DecodeKernelInfo find_decode_d128(int q_dtype, int kv_dtype, int gp);
+DecodeKernelInfo find_decode_d192(int q_dtype, int kv_dtype, int gp);
+DecodeKernelInfo find_decode_d256(int q_dtype, int kv_dtype, int gp);
 
 }  // namespace b200pa

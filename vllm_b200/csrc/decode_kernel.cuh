@@ -21,7 +21,7 @@
 //     operands these products need, so pages are used as they land, untransposed.
 //     P^T is produced from the S^T accumulators with one movmatrix per 8 tokens.
 //   * fp8 caches are dequantised after ldmatrix (4 bytes per lane) with
-//     cvt.f16x2.e4m3x2; the dot-product index order inside a 16-wide k-step is
+//     integer ALU ops (see fp8x4_to_f16); the dot-product index order inside a 16-wide k-step is
 //     permuted consistently in Q / P, which is free.  k_scale is folded into the
 //     logit scale and v_scale into the output scale.
 //   * Online softmax in the log2 domain, fp32 state, warp-shuffle reductions.
@@ -68,8 +68,8 @@ __device__ __forceinline__ int load_bt(const DecodeParams& p, const WorkItem& it
   return __ldg(p.block_tables + int64_t(it.seq) * p.max_blocks_per_seq + it.first_page + pg);
 }
 
-template <typename QT, int KV, int D, int GP>
-__global__ void __launch_bounds__(kMaxWarps * 32, 1) pa_decode_kernel(const DecodeParams p) {
+template <typename QT, int KV, int D, int GP, int MAXW, int CVT = 2>
+__global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodeParams p) {
   using TR = DecodeTraits<QT, KV, D, GP>;
   constexpr bool kFp8 = TR::kFp8;
   constexpr bool kBf = TR::kMmaBf16;
@@ -77,6 +77,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) pa_decode_kernel(const Deco
   constexpr int KS = TR::kKSteps;
   constexpr bool kE5 = KV == kCacheE5M2;
   constexpr bool kOutBf = std::is_same_v<QT, __nv_bfloat16>;
+  // fp8 unpacking pipe per operand: CVT 0 = K and V on the ALU, 1 = K on the XU and V
+  // on the ALU (balanced), 2 = both on the XU
+  constexpr bool kAluK = CVT == 0;
+  constexpr bool kAluV = CVT != 2;
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
 
@@ -102,7 +106,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) pa_decode_kernel(const Deco
 
   // ---- set-up: prefix table of partitions per sequence (exclusive scan)
   if (p.use_table) {
-    __shared__ int warp_tot[kMaxWarps];
+    __shared__ int warp_tot[MAXW];
     const int S = p.num_seqs;
     const int per = (S + blockDim.x - 1) / blockDim.x;
     const int s0 = min(S, int(threadIdx.x) * per);
@@ -162,7 +166,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) pa_decode_kernel(const Deco
     it.kvh = hsub / p.head_groups;
     it.hg = hsub % p.head_groups;
     if (p.use_table) {
-      int lo = 0, hi = p.num_seqs;  // last s with cum[s] <= cg
+      int lo = 0, hi = p.num_seqs;  // cum[lo] <= cg < cum[hi]
       while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
         if (cum[mid] <= cg) lo = mid; else hi = mid;
@@ -170,9 +174,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) pa_decode_kernel(const Deco
       it.seq = lo;
       it.part = cg - cum[lo];
       it.nparts = cum[lo + 1] - cum[lo];
-      const int len = p.seq_lens[lo];
       it.tok_begin = it.part * kPartitionTokens;
-      it.tok_end = min(len, it.tok_begin + kPartitionTokens);
+      it.tok_end = min(p.seq_lens[lo], it.tok_begin + kPartitionTokens);
     } else {
       it.seq = cg;
       it.tok_begin = 0;
@@ -226,8 +229,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) pa_decode_kernel(const Deco
 
   while (inflight < NS && produce_one()) {}
 
-  const float kv_qk = kFp8 ? *p.k_scale : 1.f;
-  const float kv_o = kFp8 ? *p.v_scale : 1.f;
+  // fp8 values come out of fp8x4_to_f16 scaled by 1/kPrescale; fold that and the
+  // per-tensor scales into the logit scale and the output scale
+  const float kv_qk = kFp8 ? *p.k_scale * Fp8Unpack<kE5, kAluK>::kPrescale : 1.f;
+  const float kv_o = kFp8 ? *p.v_scale * Fp8Unpack<kE5, kAluV>::kPrescale : 1.f;
   const float qk_scale = p.scale * kLog2e * kv_qk;
   bool failed = false;
 
@@ -317,11 +322,11 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) pa_decode_kernel(const Deco
         if (tile_tok0 >= cur.tok_end) break;
 
         // ---------------- S^T = K . Q^T
-        float s[GP][4];
+        float s[GP][4], s2[GP][4];  // two accumulation chains halve the dependent-MMA latency
 #pragma unroll
         for (int nt = 0; nt < GP; ++nt)
 #pragma unroll
-          for (int i = 0; i < 4; ++i) s[nt][i] = 0.f;
+          for (int i = 0; i < 4; ++i) s[nt][i] = s2[nt][i] = 0.f;
 
         if constexpr (!kFp8) {
           const uint32_t kaddr =
@@ -331,8 +336,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) pa_decode_kernel(const Deco
             uint32_t a0, a1, a2, a3;
             ldsm_x4(kaddr + uint32_t(2 * ks * B * 16), a0, a1, a2, a3);
 #pragma unroll
-            for (int nt = 0; nt < GP; ++nt)
-              mma16816<kBf>(s[nt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
+            for (int nt = 0; nt < GP; ++nt) {
+              if (ks & 1) mma16816<kBf>(s2[nt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
+              else mma16816<kBf>(s[nt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
+            }
           }
         } else {
           // A row rho of half h <-> token 4*(rho/2) + 2*h + rho%2
@@ -341,36 +348,34 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) pa_decode_kernel(const Deco
           const uint32_t kaddr = sk + uint32_t(((lane >> 4) * B + tt + tok) * 16);
 #pragma unroll
           for (int ks = 0; ks + 1 < KS; ks += 2) {
-            uint32_t r0, r1, r2, r3;
+            uint32_t r0, r1, r2, r3, a0, a1, a2, a3, b0, b1, b2, b3;
             ldsm_x4(kaddr + uint32_t(ks * B * 16), r0, r1, r2, r3);
-            const uint32_t a0 = fp8x2_to_f16x2<kE5>(uint16_t(r0 & 0xffff));
-            const uint32_t a2 = fp8x2_to_f16x2<kE5>(uint16_t(r0 >> 16));
-            const uint32_t a1 = fp8x2_to_f16x2<kE5>(uint16_t(r1 & 0xffff));
-            const uint32_t a3 = fp8x2_to_f16x2<kE5>(uint16_t(r1 >> 16));
-            const uint32_t b0 = fp8x2_to_f16x2<kE5>(uint16_t(r2 & 0xffff));
-            const uint32_t b2 = fp8x2_to_f16x2<kE5>(uint16_t(r2 >> 16));
-            const uint32_t b1 = fp8x2_to_f16x2<kE5>(uint16_t(r3 & 0xffff));
-            const uint32_t b3 = fp8x2_to_f16x2<kE5>(uint16_t(r3 >> 16));
+            fp8x4_to_f16<kE5, kAluK>(r0, a0, a2);
+            fp8x4_to_f16<kE5, kAluK>(r1, a1, a3);
+            fp8x4_to_f16<kE5, kAluK>(r2, b0, b2);
+            fp8x4_to_f16<kE5, kAluK>(r3, b1, b3);
 #pragma unroll
             for (int nt = 0; nt < GP; ++nt) {
               mma16816<false>(s[nt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
-              mma16816<false>(s[nt], b0, b1, b2, b3, qf[nt][ks + 1][0], qf[nt][ks + 1][1]);
+              mma16816<false>(s2[nt], b0, b1, b2, b3, qf[nt][ks + 1][0], qf[nt][ks + 1][1]);
             }
           }
           if constexpr (KS & 1) {
             constexpr int ks = KS - 1;
-            uint32_t r0, r1;
+            uint32_t r0, r1, a0, a1, a2, a3;
             // lanes 0-15 supply the addresses of the two matrices (lanes 16-31 ignored)
             ldsm_x2(sk + uint32_t((ks * B + tt + tok) * 16), r0, r1);
-            const uint32_t a0 = fp8x2_to_f16x2<kE5>(uint16_t(r0 & 0xffff));
-            const uint32_t a2 = fp8x2_to_f16x2<kE5>(uint16_t(r0 >> 16));
-            const uint32_t a1 = fp8x2_to_f16x2<kE5>(uint16_t(r1 & 0xffff));
-            const uint32_t a3 = fp8x2_to_f16x2<kE5>(uint16_t(r1 >> 16));
+            fp8x4_to_f16<kE5, kAluK>(r0, a0, a2);
+            fp8x4_to_f16<kE5, kAluK>(r1, a1, a3);
 #pragma unroll
             for (int nt = 0; nt < GP; ++nt)
               mma16816<false>(s[nt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
           }
         }
+#pragma unroll
+        for (int nt = 0; nt < GP; ++nt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) s[nt][i] += s2[nt][i];
 
         // ---------------- scale, ALiBi, mask
         int tok_lo, tok_hi;  // absolute token of accumulator rows g and g+8
@@ -462,16 +467,12 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) pa_decode_kernel(const Deco
               sv + uint32_t((16 * (lane >> 4) + ((lane >> 3) & 1) * 8 + (lane & 7)) * B + tt);
 #pragma unroll
           for (int mt = 0; mt + 1 < KS; mt += 2) {
-            uint32_t r0, r1, r2, r3;
+            uint32_t r0, r1, r2, r3, a0, a1, a2, a3, b0, b1, b2, b3;
             ldsm_x4(vaddr + uint32_t(16 * mt * B), r0, r1, r2, r3);
-            const uint32_t a0 = fp8x2_to_f16x2<kE5>(uint16_t(r0 & 0xffff));
-            const uint32_t a2 = fp8x2_to_f16x2<kE5>(uint16_t(r0 >> 16));
-            const uint32_t a1 = fp8x2_to_f16x2<kE5>(uint16_t(r1 & 0xffff));
-            const uint32_t a3 = fp8x2_to_f16x2<kE5>(uint16_t(r1 >> 16));
-            const uint32_t b0 = fp8x2_to_f16x2<kE5>(uint16_t(r2 & 0xffff));
-            const uint32_t b2 = fp8x2_to_f16x2<kE5>(uint16_t(r2 >> 16));
-            const uint32_t b1 = fp8x2_to_f16x2<kE5>(uint16_t(r3 & 0xffff));
-            const uint32_t b3 = fp8x2_to_f16x2<kE5>(uint16_t(r3 >> 16));
+            fp8x4_to_f16<kE5, kAluV>(r0, a0, a2);
+            fp8x4_to_f16<kE5, kAluV>(r1, a1, a3);
+            fp8x4_to_f16<kE5, kAluV>(r2, b0, b2);
+            fp8x4_to_f16<kE5, kAluV>(r3, b1, b3);
 #pragma unroll
             for (int nt = 0; nt < GP; ++nt) {
               mma16816<false>(o[mt][nt], a0, a1, a2, a3, pf[nt][0], pf[nt][1]);
@@ -480,12 +481,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) pa_decode_kernel(const Deco
           }
           if constexpr (KS & 1) {
             constexpr int mt = KS - 1;
-            uint32_t r0, r1;
+            uint32_t r0, r1, a0, a1, a2, a3;
             ldsm_x2(sv + uint32_t((16 * mt + ((lane >> 3) & 1) * 8 + (lane & 7)) * B + tt), r0, r1);
-            const uint32_t a0 = fp8x2_to_f16x2<kE5>(uint16_t(r0 & 0xffff));
-            const uint32_t a2 = fp8x2_to_f16x2<kE5>(uint16_t(r0 >> 16));
-            const uint32_t a1 = fp8x2_to_f16x2<kE5>(uint16_t(r1 & 0xffff));
-            const uint32_t a3 = fp8x2_to_f16x2<kE5>(uint16_t(r1 >> 16));
+            fp8x4_to_f16<kE5, kAluV>(r0, a0, a2);
+            fp8x4_to_f16<kE5, kAluV>(r1, a1, a3);
 #pragma unroll
             for (int nt = 0; nt < GP; ++nt)
               mma16816<false>(o[mt][nt], a0, a1, a2, a3, pf[nt][0], pf[nt][1]);
@@ -545,6 +544,74 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) pa_decode_kernel(const Deco
           QT* orow = obase + hl_t * ohead_stride + 16 * mt + 2 * c;
           *reinterpret_cast<uint32_t*>(orow) = lo;
           *reinterpret_cast<uint32_t*>(orow + 8) = hi;
+        }
+      }
+    }
+
+    // ---- split sequences: the warp that delivers the LAST partial of a (sequence, kv head,
+    // head group) merges all of them into `out` (replaces the reference's separate
+    // paged_attention_v2_reduce_kernel launch, attention_kernels.cuh:559-664).  Nobody waits:
+    // earlier arrivers just leave.
+    if (!direct && p.arrive != nullptr) {
+      __threadfence();  // partials visible before the arrival is counted
+      __syncwarp();
+      unsigned* cnt = p.arrive + (size_t(cur.seq) * p.num_kv_heads + cur.kvh) * p.head_groups + cur.hg;
+      unsigned old = 0;
+      if (lane == 0) old = atomicAdd(cnt, 1u);
+      old = __shfl_sync(0xffffffffu, old, 0);
+      if (old == unsigned(cur.nparts - 1)) {
+        if (lane == 0) *cnt = 0;  // re-arm for the next launch
+        __threadfence();          // order the loads below after the observed arrivals
+        const int np = cur.nparts;
+        const int P = p.max_partitions;
+        // Work unit = 8 consecutive output elements (16 bytes) of one head; lane takes
+        // units lane, lane+32, ...  All loads of a unit's partitions are independent, so
+        // the merge costs a couple of L2 round trips rather than one per partition.
+        constexpr int UPH = D / 8;  // units per head
+        const int units = nheads * UPH;
+        for (int u = lane; u < units; u += 32) {
+          const int hl = u / UPH;
+          const int e0 = (u % UPH) * 8;
+          const int64_t row = (int64_t(cur.seq) * p.num_heads + hq0 + hl) * P;
+          const float* ml = p.max_logits + row;
+          const float* es = p.exp_sums + row;
+          float mx = -INFINITY;
+#pragma unroll 4
+          for (int j = 0; j < np; ++j) mx = fmaxf(mx, __ldcg(ml + j));
+          float acc[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+          float wsum = 0.f;
+          const QT* src = static_cast<const QT*>(p.tmp_out) + row * D + e0;
+#pragma unroll 4
+          for (int j = 0; j < np; ++j) {
+            const float w = __ldcg(es + j) * fast_exp2(__ldcg(ml + j) - mx);
+            const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src + int64_t(j) * D));
+            wsum += w;
+            const uint32_t vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              float f0, f1;
+              if constexpr (kOutBf) {
+                f0 = __uint_as_float(vv[i] << 16);
+                f1 = __uint_as_float(vv[i] & 0xffff0000u);
+              } else {
+                const __half2 h = *reinterpret_cast<const __half2*>(&vv[i]);
+                f0 = __low2float(h);
+                f1 = __high2float(h);
+              }
+              acc[2 * i] += w * f0;
+              acc[2 * i + 1] += w * f1;
+            }
+          }
+          const float winv = __fdividef(1.f, wsum + 1e-6f);
+          uint4 o4;
+          o4.x = pack2<kOutBf>(acc[0] * winv, acc[1] * winv);
+          o4.y = pack2<kOutBf>(acc[2] * winv, acc[3] * winv);
+          o4.z = pack2<kOutBf>(acc[4] * winv, acc[5] * winv);
+          o4.w = pack2<kOutBf>(acc[6] * winv, acc[7] * winv);
+          *reinterpret_cast<uint4*>(static_cast<QT*>(p.out) +
+                                    (int64_t(cur.seq) * p.num_heads + hq0 + hl) * D + e0) = o4;
         }
       }
     }

@@ -184,20 +184,37 @@ pa_generic_kernel(const DecodeParams p, int head_size, int x) {
 
 // ------------------------------------------------------------------ host side
 __device__ unsigned g_sched_words[256][2];  // zero-initialised; self-resetting per launch
+// Arrival counters of the fused split-KV merge: one per (sequence, kv head, head
+// group); zero-initialised and re-armed by the warp that performs the merge.
+constexpr int kArriveRegions = 8;
+constexpr int kArrivePerRegion = 16384;
+__device__ unsigned g_arrive[kArriveRegions][kArrivePerRegion];
 
-static unsigned* sched_slot() {
+// Picks the scheduler words (256 rotating slots) and the arrival-counter region
+// (8 rotating regions) of one launch.  Rotation keeps launches that overlap on
+// different streams apart; launches on one stream are ordered anyway.
+static bool launch_slots(unsigned** sched, unsigned** arrive) {
   constexpr int kMaxDev = 64;
-  static unsigned* base[kMaxDev] = {};
+  static unsigned* sbase[kMaxDev] = {};
+  static unsigned* abase[kMaxDev] = {};
   static std::atomic<unsigned> rr{0};
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return nullptr;
-  unsigned* b = __atomic_load_n(&base[dev], __ATOMIC_ACQUIRE);
-  if (b == nullptr) {
-    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&b), g_sched_words) != cudaSuccess)
-      return nullptr;
-    __atomic_store_n(&base[dev], b, __ATOMIC_RELEASE);
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return false;
+  unsigned* sb = __atomic_load_n(&sbase[dev], __ATOMIC_ACQUIRE);
+  unsigned* ab = __atomic_load_n(&abase[dev], __ATOMIC_ACQUIRE);
+  if (sb == nullptr || ab == nullptr) {
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&sb), g_sched_words) != cudaSuccess ||
+        cudaGetSymbolAddress(reinterpret_cast<void**>(&ab), g_arrive) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return false;
+    }
+    __atomic_store_n(&abase[dev], ab, __ATOMIC_RELEASE);
+    __atomic_store_n(&sbase[dev], sb, __ATOMIC_RELEASE);
   }
-  return b + 2 * (rr.fetch_add(1, std::memory_order_relaxed) & 255u);
+  const unsigned slot = rr.fetch_add(1, std::memory_order_relaxed);
+  *sched = sb + 2 * (slot & 255u);
+  *arrive = ab + size_t(slot % kArriveRegions) * kArrivePerRegion;
+  return true;
 }
 
 static int sm_count() {
@@ -213,7 +230,7 @@ static int sm_count() {
   return cache[dev];
 }
 
-static DecodeLaunchFn find_decode(int d, int qdt, int kv, int gp) {
+static DecodeKernelInfo find_decode(int d, int qdt, int kv, int gp) {
   switch (d) {
     case 32: return find_decode_d32(qdt, kv, gp);
     case 64: return find_decode_d64(qdt, kv, gp);
@@ -224,7 +241,7 @@ static DecodeLaunchFn find_decode(int d, int qdt, int kv, int gp) {
     case 192: return find_decode_d192(qdt, kv, gp);
     case 256: return find_decode_d256(qdt, kv, gp);
   }
-  return nullptr;
+  return {nullptr, 0};
 }
 
 template <typename QT>
@@ -359,15 +376,17 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
   const int es = a->kv_dtype == B200PA_KV_AUTO ? 2 : 1;
   auto aligned = [](const void* ptr, uintptr_t n) { return reinterpret_cast<uintptr_t>(ptr) % n == 0; };
   const int gp = p.group <= 8 ? 1 : 2;
-  DecodeLaunchFn fn = nullptr;
+  DecodeKernelInfo ki{nullptr, 0};
   bool fast = !force_generic() && a->q_dtype != B200PA_F32 &&
               (a->block_size == 16 || a->block_size == 32) && a->head_size % 16 == 0 &&
               aligned(a->key_cache, 16) && aligned(a->value_cache, 16) && aligned(a->query, 16) &&
               aligned(a->out, 16) && (!split || aligned(a->tmp_out, 16)) &&
               (a->kv_block_stride * es) % 16 == 0 && (a->kv_head_stride * es) % 16 == 0 &&
               a->q_stride % 8 == 0;
-  if (fast) fn = find_decode(a->head_size, a->q_dtype, a->kv_dtype, gp);
+  if (fast) ki = find_decode(a->head_size, a->q_dtype, a->kv_dtype, gp);
+  DecodeLaunchFn fn = ki.fn;
   int rc;
+  bool fused = false;
   if (fn != nullptr) {
     p.head_groups = (p.group + 8 * gp - 1) / (8 * gp);
     const size_t stage_bytes = size_t(2) * a->head_size * a->block_size * es;
@@ -381,21 +400,34 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
       return B200PA_EUNSUPPORTED;
     }
     const size_t budget = budget_total - table_bytes - 1024 /* mbarriers */;
-    int nwarps = int(std::min<size_t>(kMaxWarps, budget / (3 * stage_bytes)));
+    // Warps hide the latency of the per-page compute chain, stages the latency of HBM.
+    // Measured on B200: 16-bit caches run best with two stages per warp and as many
+    // warps as then fit (12 x 2 x 8 KiB for head size 128, block size 16); fp8 caches
+    // carry twice the instructions per byte and want the most warps first, even with a
+    // single stage.  B200PA_TUNE_WARPS / B200PA_TUNE_STAGES override the choice.
+    const size_t min_stages = es == 1 ? 1 : 2;
+    int nwarps = int(std::min<size_t>(size_t(ki.max_warps), budget / (min_stages * stage_bytes)));
+    if (nwarps > 4) nwarps &= ~3;  // same number of warps on each of the 4 schedulers
     if (nwarps < 1) nwarps = 1;
-    int ns = int(std::min<size_t>(8, budget / (size_t(nwarps) * stage_bytes)));
-    if (ns < 2) {
+    if (const char* e = getenv("B200PA_TUNE_WARPS"))
+      nwarps = std::max(1, std::min(ki.max_warps, atoi(e)));
+    int ns = int(std::min<size_t>(4, budget / (size_t(nwarps) * stage_bytes)));
+    if (const char* e = getenv("B200PA_TUNE_STAGES")) ns = std::max(1, std::min(ns, atoi(e)));
+    if (ns < 1) {
       set_error("head_size=%d block_size=%d does not fit the shared-memory pipeline", a->head_size,
                 a->block_size);
       return B200PA_EUNSUPPORTED;
     }
     p.nstages = ns;
-    p.sched = sched_slot();
+    unsigned* arrive = nullptr;
     p.status = device_status_ptr();
-    if (p.sched == nullptr || p.status == nullptr) {
+    if (!launch_slots(&p.sched, &arrive) || p.status == nullptr) {
       set_error("could not resolve device-side scheduler/status words");
       return B200PA_ECUDA;
     }
+    // merge the partials inside the decode kernel when the counters cover the batch
+    fused = split && int64_t(p.num_seqs) * p.num_kv_heads * p.head_groups <= kArrivePerRegion;
+    p.arrive = fused ? arrive : nullptr;
     const size_t bars_bytes = (size_t(nwarps) * ns * 8 + 127) & ~size_t(127);
     const size_t smem = table_bytes + bars_bytes + size_t(nwarps) * ns * stage_bytes;
     const int grid = sm_count();
@@ -418,7 +450,7 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
     }
   }
   if (rc != B200PA_OK) return rc;
-  if (split) {
+  if (split && !fused) {
     switch (a->q_dtype) {
       case B200PA_F32: return launch_reduce<float>(p, a->head_size, s);
       case B200PA_F16: return launch_reduce<__half>(p, a->head_size, s);
