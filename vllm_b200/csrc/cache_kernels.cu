@@ -6,9 +6,11 @@
 // The work is pure data movement, so the design goal is full-sector traffic:
 //   * x-layout K: one 16-byte store per (token, head, d/x) chunk.
 //   * x-layout V is a transpose ([token][d] -> [d][token-in-block]).  A CTA owns
-//     a tile of 16 consecutive tokens; each thread owns one (head, d) row and
-//     writes every run of tokens that landed in consecutive slots of one block
-//     with the widest aligned store (16 B for a full fp8 run), instead of one
+//     a tile of 16 consecutive tokens.  When the tile fills 16 consecutive slots
+//     of one block (prefill, chunked writes) a thread reads 16 bytes of 8 d per
+//     token and writes 8 rows of 16 tokens with 16-byte stores; otherwise each
+//     thread owns one (head, d) row and writes every run of tokens that landed
+//     in consecutive slots with the widest aligned store, instead of one
 //     1-2 byte store per element.
 //   * flash layout: 16-byte vector row copies, NHD or HND by strides.
 // Quantisation is cvt.rn.satfinite of an IEEE fp32 division, bit-identical to
@@ -77,6 +79,11 @@ reshape_and_cache_kernel(const in_t* __restrict__ key, const in_t* __restrict__ 
   const float v_scale = (KV == kKvAuto) ? 1.f : *v_scale_ptr;
   const int chunks = head_size / x;  // per head
   const int hd = num_heads * head_size;
+  // 16-byte loads from key/value rows are legal when bases and row strides are 16-byte multiples
+  const bool in_vec_ok =
+      ((reinterpret_cast<uintptr_t>(key) | reinterpret_cast<uintptr_t>(value) |
+        (size_t(key_stride) * sizeof(in_t)) | (size_t(value_stride) * sizeof(in_t)) |
+        (size_t(head_size) * sizeof(in_t)) | (size_t(x) * sizeof(in_t))) & 15) == 0;
 
   // ---- K: work item = (token, head, chunk); chunk fastest for coalesced reads.
   const int k_items = ntok * num_heads * chunks;
@@ -93,14 +100,69 @@ reshape_and_cache_kernel(const in_t* __restrict__ key, const in_t* __restrict__ 
                    int64_t(off) * x;
     // x elements = 16 bytes of cache in the standard layout; handle any x generically.
     if (x * int(sizeof(cache_t)) == 16 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-      constexpr int N = 16 / sizeof(cache_t);
+      constexpr int N = 16 / sizeof(cache_t);        // elements per 16-byte store
+      constexpr int L = N * sizeof(in_t) / 16;       // 16-byte loads that feed it
+      in_t in[N];
+      if (in_vec_ok) {
+#pragma unroll
+        for (int i = 0; i < L; ++i)
+          reinterpret_cast<uint4*>(in)[i] = reinterpret_cast<const uint4*>(src)[i];
+      } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) in[i] = src[i];
+      }
       cache_t vals[N];
 #pragma unroll
-      for (int i = 0; i < N; ++i) vals[i] = store_convert<in_t, cache_t, KV>(src[i], k_scale);
+      for (int i = 0; i < N; ++i) vals[i] = store_convert<in_t, cache_t, KV>(in[i], k_scale);
       *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(vals);
     } else {
       for (int i = 0; i < x; ++i) dst[i] = store_convert<in_t, cache_t, KV>(src[i], k_scale);
     }
+  }
+
+  // ---- V fast path: the whole tile is one run that fills slots [off, off+16) of one block
+  // (prefill / chunked writes).  A thread takes VD consecutive d of one head, reads them
+  // for the 16 tokens with 16-byte loads and writes VD rows of 16 tokens each.
+  constexpr int VD = 16 / sizeof(in_t);
+  bool full_run = ntok == kTokTile && in_vec_ok && head_size % VD == 0 && block_size % kTokTile == 0;
+  if (full_run) {
+    const int64_t s0 = s_slot[0];
+    full_run = s0 >= 0 && (s0 % kTokTile) == 0;
+#pragma unroll
+    for (int i = 1; i < kTokTile; ++i) full_run = full_run && s_slot[i] == s0 + i;
+    full_run = full_run &&
+               ((reinterpret_cast<uintptr_t>(value_cache) | (size_t(block_size) * sizeof(cache_t))) &
+                (kTokTile * sizeof(cache_t) >= 16 ? 15 : (kTokTile * sizeof(cache_t) - 1))) == 0;
+  }
+  if (full_run) {
+    const int64_t s0 = s_slot[0];
+    const int64_t b = s0 / block_size;
+    const int off = int(s0 % block_size);
+    const int groups = hd / VD;
+    for (int gidx = threadIdx.x; gidx < groups; gidx += blockDim.x) {
+      const int row0 = gidx * VD;  // (head, d) flattened; a group never straddles a head
+      const in_t* src = value + int64_t(tok0) * value_stride + row0;
+      cache_t vals[VD][kTokTile];
+#pragma unroll
+      for (int t = 0; t < kTokTile; ++t) {
+        in_t in[VD];
+        *reinterpret_cast<uint4*>(in) = *reinterpret_cast<const uint4*>(src + int64_t(t) * value_stride);
+#pragma unroll
+        for (int d = 0; d < VD; ++d) vals[d][t] = store_convert<in_t, cache_t, KV>(in[d], v_scale);
+      }
+      cache_t* dst = value_cache + (b * hd + row0) * int64_t(block_size) + off;
+#pragma unroll
+      for (int d = 0; d < VD; ++d) {
+        constexpr int W = kTokTile * sizeof(cache_t) / 16;  // 16-byte stores per row (0 for 1-byte x 8...)
+        if constexpr (W >= 1) {
+#pragma unroll
+          for (int w = 0; w < W; ++w)
+            reinterpret_cast<uint4*>(dst + int64_t(d) * block_size)[w] =
+                reinterpret_cast<const uint4*>(vals[d])[w];
+        }
+      }
+    }
+    return;
   }
 
   // ---- V: thread owns one (head, d) row of the tile; writes runs of consecutive slots.
