@@ -35,7 +35,8 @@ struct DecodeParams {
   int num_kv_heads;
   int block_size;
   int max_blocks_per_seq;
-  int max_partitions;  // P; 0 = unsplit (v1): one work item covers the whole sequence
+  int max_partitions;  // P; 0 = unsplit: one work item covers the whole sequence
+  int part_tokens;     // tokens per partition (512 for v2; v1 may split finer into library scratch)
   int group;           // query heads per kv head
   int head_groups;     // ceil(group / heads per item)
   int nstages;

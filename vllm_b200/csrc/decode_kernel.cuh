@@ -91,6 +91,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
   const int c = lane & 3;   // fragment column pair
   const int B = p.block_size;
   const int NS = p.nstages;
+  const int PT = p.part_tokens;  // tokens per split-KV partition (a multiple of the block size)
   const uint32_t page_bytes = uint32_t(D) * B * ES;
   const uint32_t stage_bytes = 2 * page_bytes;
 
@@ -114,7 +115,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
     int mine = 0;
     for (int s = s0; s < s1; ++s) {
       const int len = p.seq_lens[s];
-      mine += max(1, (len + kPartitionTokens - 1) / kPartitionTokens);
+      mine += max(1, (len + PT - 1) / PT);
     }
     int incl = mine;
 #pragma unroll
@@ -130,7 +131,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
     for (int s = s0; s < s1; ++s) {
       cum[s] = run;
       const int len = p.seq_lens[s];
-      run += max(1, (len + kPartitionTokens - 1) / kPartitionTokens);
+      run += max(1, (len + PT - 1) / PT);
     }
     if (threadIdx.x == blockDim.x - 1) cum[S] = run;
   }
@@ -174,8 +175,8 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
       it.seq = lo;
       it.part = cg - cum[lo];
       it.nparts = cum[lo + 1] - cum[lo];
-      it.tok_begin = it.part * kPartitionTokens;
-      it.tok_end = min(p.seq_lens[lo], it.tok_begin + kPartitionTokens);
+      it.tok_begin = it.part * PT;
+      it.tok_end = min(p.seq_lens[lo], it.tok_begin + PT);
     } else {
       it.seq = cg;
       it.tok_begin = 0;

@@ -22,7 +22,7 @@ __global__ void pa_reduce_kernel(QT* __restrict__ out, const QT* __restrict__ tm
                                  const float* __restrict__ exp_sums,
                                  const float* __restrict__ max_logits,
                                  const int* __restrict__ seq_lens, int num_seqs, int num_heads,
-                                 int head_size, int max_partitions) {
+                                 int head_size, int max_partitions, int part_tokens) {
   extern __shared__ float s_w[];  // [warps][max_partitions]
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -30,7 +30,7 @@ __global__ void pa_reduce_kernel(QT* __restrict__ out, const QT* __restrict__ tm
   if (item >= num_seqs * num_heads) return;
   const int seq = item / num_heads;
   const int len = seq_lens[seq];
-  const int np = (len + kPartitionTokens - 1) / kPartitionTokens;
+  const int np = (len + part_tokens - 1) / part_tokens;
   if (np <= 1) return;
   float* w = s_w + warp * max_partitions;
   const float* ml = max_logits + int64_t(item) * max_partitions;
@@ -88,10 +88,11 @@ pa_generic_kernel(const DecodeParams p, int head_size, int x) {
   const int seq = int(item / (int64_t(P) * p.num_heads));
   const int len = p.seq_lens[seq];
   const bool split = p.max_partitions > 0;
-  const int nparts = split ? max(1, (len + kPartitionTokens - 1) / kPartitionTokens) : 1;
+  const int PT = p.part_tokens;
+  const int nparts = split ? max(1, (len + PT - 1) / PT) : 1;
   if (part >= nparts) return;
-  const int t0 = split ? part * kPartitionTokens : 0;
-  const int t1 = split ? min(len, t0 + kPartitionTokens) : len;
+  const int t0 = split ? part * PT : 0;
+  const int t1 = split ? min(len, t0 + PT) : len;
   const int B = p.block_size;
   const int kvh = head / p.group;
   const float kq = KV == kCache16 ? 1.f : *p.k_scale;
@@ -190,6 +191,30 @@ constexpr int kArriveRegions = 8;
 constexpr int kArrivePerRegion = 16384;
 __device__ unsigned g_arrive[kArriveRegions][kArrivePerRegion];
 
+// Split-KV workspace of paged_attention_v1.  The reference's v1 has no scratch
+// argument, so a sequence could only be handled by one work item; with a small batch
+// that leaves most of the GPU idle.  v1 therefore splits sequences into partitions of
+// 64..512 tokens when the partials fit this buffer, exactly like v2 does with the
+// caller's scratch.  Shared by all v1 calls on a device (one stream at a time).
+constexpr size_t kV1ScratchBytes = size_t(32) << 20;
+static __device__ __align__(256) unsigned char g_v1_scratch[kV1ScratchBytes];
+
+static unsigned char* v1_scratch_ptr() {
+  constexpr int kMaxDev = 64;
+  static unsigned char* cache[kMaxDev] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return nullptr;
+  unsigned char* ptr = __atomic_load_n(&cache[dev], __ATOMIC_ACQUIRE);
+  if (ptr == nullptr) {
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_v1_scratch) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    __atomic_store_n(&cache[dev], ptr, __ATOMIC_RELEASE);
+  }
+  return ptr;
+}
+
 // Picks the scheduler words (256 rotating slots) and the arrival-counter region
 // (8 rotating regions) of one launch.  Rotation keeps launches that overlap on
 // different streams apart; launches on one stream are ordered anyway.
@@ -278,7 +303,7 @@ static int launch_reduce(const DecodeParams& p, int head_size, cudaStream_t s) {
   const size_t smem = size_t(warps) * p.max_partitions * sizeof(float);
   pa_reduce_kernel<QT><<<grid, warps * 32, smem, s>>>(
       static_cast<QT*>(p.out), static_cast<const QT*>(p.tmp_out), p.exp_sums, p.max_logits,
-      p.seq_lens, p.num_seqs, p.num_heads, head_size, p.max_partitions);
+      p.seq_lens, p.num_seqs, p.num_heads, head_size, p.max_partitions, p.part_tokens);
   count_launch();
   B200PA_CHECK_CUDA(cudaGetLastError());
   return B200PA_OK;
@@ -367,8 +392,9 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
   p.block_size = a->block_size;
   p.max_blocks_per_seq = a->max_num_blocks_per_seq;
   // a single partition needs no scratch and no reduce: run it unsplit
-  const bool split = v2 && a->max_num_partitions > 1;
+  bool split = v2 && a->max_num_partitions > 1;
   p.max_partitions = split ? a->max_num_partitions : 0;
+  p.part_tokens = kPartitionTokens;
   p.group = a->num_heads / a->num_kv_heads;
   p.scale = a->scale;
 
@@ -392,6 +418,31 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
     const size_t stage_bytes = size_t(2) * a->head_size * a->block_size * es;
     // The partition prefix table lives in shared memory; very large batches run
     // without it (one work item per sequence and kv head).
+    if (!split && a->max_seq_len > 64 && p.num_seqs <= 12000 &&
+        !getenv("B200PA_TUNE_NO_V1_SPLIT")) {
+      // No caller scratch (v1, or v2 with a single 512-token partition): split into the
+      // library's own workspace.  Partition size: 512 tokens, refined down to 64 while the
+      // batch still has fewer than ~4 work items per resident warp.
+      const int64_t warps_total = int64_t(sm_count()) * 12;
+      const int64_t units = int64_t(p.num_seqs) * p.num_kv_heads * p.head_groups;
+      int pt = kPartitionTokens;
+      while (pt > 64 && units * ((a->max_seq_len + pt / 2 - 1) / (pt / 2)) <= 4 * warps_total) pt /= 2;
+      const int64_t parts = (int64_t(a->max_seq_len) + pt - 1) / pt;
+      const int64_t n = int64_t(p.num_seqs) * p.num_heads * parts;
+      auto up = [](int64_t v) { return (v + 255) & ~int64_t(255); };
+      const int64_t stat = up(n * 4);
+      const int64_t need = 2 * stat + up(n * a->head_size * 2);
+      unsigned char* ws = (parts > 1 && need <= int64_t(kV1ScratchBytes) &&
+                           units <= kArrivePerRegion) ? v1_scratch_ptr() : nullptr;
+      if (ws != nullptr) {
+        split = true;
+        p.part_tokens = pt;
+        p.max_partitions = int(parts);
+        p.exp_sums = reinterpret_cast<float*>(ws);
+        p.max_logits = reinterpret_cast<float*>(ws + stat);
+        p.tmp_out = ws + 2 * stat;
+      }
+    }
     p.use_table = split ? 1 : 0;
     size_t table_bytes = p.use_table ? size_t((p.num_seqs + 1 + 3) & ~3) * 4 : 0;
     const size_t budget_total = 227 * 1024 - 1024;  // static smem + slack
