@@ -43,8 +43,9 @@ METRIC = "paged_attention decode tokens/s"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode-kernel launch divided by the
 # algorithmic bytes of that launch, from the ncu capture summarised in
-# profiles/pa_decode_kernel_cfg2_small.md (traffic grows in proportion to tokens).
-NCU_TRAFFIC_RATIO = {"cfg2": None}
+# profiles/pa_decode_kernel_cfg2.md and profiles/pa_decode_kernel_cfg3_fp8.md (small cases of the
+# same kernels; traffic grows in proportion to tokens).
+NCU_TRAFFIC_RATIO = {"cfg2": 1.015, "cfg4": 1.015, "cfg3": 1.020, "cfg5": 1.020}
 
 
 def measured_peak():
@@ -351,7 +352,7 @@ def main() -> int:
                 "frac_of_nominal_8TBs": achieved / 8000.0,
                 "traffic": None if ratio is None else ratio * bytes_rank,
                 "algorithmic_bytes_per_launch": int(bytes_rank),
-                "kernel": "pa_decode_kernel (+ pa_reduce_kernel; the op's two launches are timed together)",
+                "kernel": "pa_decode_kernel (split-KV merge fused; one launch per step)",
                 "ms_min": float(np.min(per_step)), "ms_median": float(np.median(per_step)),
             },
             "wall_s_timed_region": t_wall,
