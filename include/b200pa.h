@@ -9,6 +9,8 @@
  *   torch.ops._C_cache_ops.reshape_and_cache   csrc/torch_bindings.cpp:687-694
  *   torch.ops._C_cache_ops.reshape_and_cache_flash          ... :696-705
  *   torch.ops._C_cache_ops.convert_fp8         csrc/torch_bindings.cpp:716-719
+ * and, next to that path, torch.ops._C.merge_attn_states (csrc/torch_bindings.cpp:83-90),
+ * torch.ops._C_cache_ops.copy_blocks / swap_blocks (csrc/torch_bindings.cpp:672-685).
  *
  * Conventions
  *   - Plain C: raw device pointers, sizes and element strides; no framework
@@ -214,6 +216,44 @@ int b200pa_reshape_and_cache_flash(const b200pa_cache_args* args, void* stream);
 int b200pa_convert_fp8(void* dst, const void* src, int64_t numel, float scale,
                        int32_t wide_dtype, int32_t kv_dtype, int32_t to_fp8,
                        void* stream);
+
+/*
+ * Replaces merge_attn_states (csrc/attention/merge_attn_states.cu:14-212, schema
+ * csrc/torch_bindings.cpp:83-90): merges two partial attention results with their
+ * log-sum-exp,
+ *   out = (prefix * e^(p_lse-m) + suffix * e^(s_lse-m)) / (e^(p_lse-m) + e^(s_lse-m)),
+ *   out_lse = log(sum) + m,  m = max(p_lse, s_lse);  infinite LSEs count as -inf and
+ *   if both are, prefix_output is passed through.
+ * output / prefix_output / suffix_output: [num_tokens, num_heads, head_size] contiguous,
+ * 16-byte aligned, of `dtype` (b200pa_dtype); *_lse: [num_heads, num_tokens] float32;
+ * output_lse may be NULL.  head_size must be a multiple of 16 / sizeof(element).
+ */
+int b200pa_merge_attn_states(void* output, float* output_lse, const void* prefix_output,
+                             const float* prefix_lse, const void* suffix_output,
+                             const float* suffix_lse, int64_t num_tokens, int32_t num_heads,
+                             int32_t head_size, int32_t dtype, void* stream);
+
+/*
+ * Replaces copy_blocks (csrc/cache_kernels.cu:73-171): for every layer l and every
+ * pair (src, dst) in block_mapping, copies block src to block dst inside
+ * key_caches[l] and inside value_caches[l].  key_caches / value_caches are HOST
+ * arrays of num_layers device pointers; block_mapping is a DEVICE array of
+ * num_pairs (src, dst) int64 pairs; block_bytes is the size of one block of one
+ * cache in bytes.  The pointers are passed to the kernel as parameters: no device
+ * allocation, no host-device copy, no synchronisation.
+ */
+int b200pa_copy_blocks(void* const* key_caches, void* const* value_caches, int32_t num_layers,
+                       const int64_t* block_mapping, int64_t num_pairs, int64_t block_bytes,
+                       void* stream);
+
+/*
+ * Replaces swap_blocks (csrc/cache_kernels.cu:26-69): copies block src -> dst for
+ * every (src, dst) int64 pair of the HOST array block_mapping_host, between two
+ * caches that may live on the host or on the current device (one asynchronous copy
+ * per block on `stream`; pinned host memory is needed for true asynchrony).
+ */
+int b200pa_swap_blocks(const void* src, void* dst, const int64_t* block_mapping_host,
+                       int64_t num_pairs, int64_t block_bytes, void* stream);
 
 /* Thread-local message for the last non-zero return on this thread ("" if none). */
 const char* b200pa_last_error(void);

@@ -158,15 +158,36 @@ def _attend_ref(q, k, v, scale, slopes, seq_len, tok0, T):
     return out, m, l
 
 
+def blocksparse_mask(seq_len, block_size, num_heads, num_kv_heads, tp_rank, local_blocks,
+                     vert_stride, bs_block_size, head_sliding_step):
+    """[Hq, seq_len] bool: which tokens a head attends to under the reference's block-sparse
+    pattern (csrc/attention/attention_kernels.cuh:204-251): a KV block is kept when it is one
+    of the last `local_blocks` sparse blocks or every `vert_stride`-th one, shifted per head."""
+    tok = torch.arange(seq_len)
+    kb = (tok // block_size) * block_size // bs_block_size
+    q_blk = (seq_len - 1) // bs_block_size
+    g = num_heads // num_kv_heads
+    rows = []
+    for h in range(num_heads):
+        if head_sliding_step >= 0:
+            off = (tp_rank * num_heads + h) * head_sliding_step + 1
+        else:
+            off = (tp_rank * num_kv_heads + h // g) * (-head_sliding_step) + 1
+        rows.append(((kb + off) % vert_stride == 0) | (kb > q_blk - local_blocks))
+    return torch.stack(rows, 0)
+
+
 def paged_attention(query, key_cache, value_cache, num_kv_heads, scale, block_tables, seq_lens,
                     alibi_slopes=None, kv_cache_dtype="auto", k_scale=1.0, v_scale=1.0,
-                    mode="ref", partition_size=None, seqs=None):
+                    mode="ref", partition_size=None, seqs=None, blocksparse=None):
     """Decode attention over a paged KV cache; returns ``out`` [S, Hq, D].
 
     mode="ref": reference rounding points, result in the query dtype.
     mode="f64": float64 mathematics, result in float64.
     partition_size: None = one pass per sequence (v1); an int = v2 split + reduce.
     seqs: optional iterable of sequence indices to compute (others are left zero).
+    blocksparse: None or (tp_rank, local_blocks, vert_stride, block_size, head_sliding_step);
+        only with mode="f64" (masked tokens get zero weight).
     """
     S, Hq, D = query.shape
     G = Hq // num_kv_heads
@@ -190,6 +211,9 @@ def paged_attention(query, key_cache, value_cache, num_kv_heads, scale, block_ta
             if alibi_slopes is not None:
                 pos = torch.arange(L, dtype=torch.float64) - L + 1
                 logits = logits + alibi_slopes.view(-1, 1).double() * pos.view(1, -1)
+            if blocksparse is not None:
+                keep = blocksparse_mask(L, value_cache.shape[3], Hq, num_kv_heads, *blocksparse)
+                logits = logits.masked_fill(~keep, -math.inf)
             p = torch.softmax(logits, dim=1)
             out[s] = torch.einsum("hn,nhd->hd", p, v.double())
             continue
@@ -228,3 +252,39 @@ def attn_bytes(seq_lens, num_heads, num_kv_heads, head_size, block_size, q_bytes
     qo = 2 * len(lens) * num_heads * head_size * q_bytes
     bt = 4 * sum((n + block_size - 1) // block_size for n in lens) + 4 * len(lens)
     return kv + qo + bt
+
+
+def merge_attn_states(prefix_output, prefix_lse, suffix_output, suffix_lse):
+    """LSE-weighted merge of two partial attention results
+    (csrc/attention/merge_attn_states.cu:14-114): outputs [T, H, D], lse [H, T].
+    Infinite LSEs count as -inf; when both are, the prefix passes through.
+    Returns (output in the input dtype, output_lse float32)."""
+    p_lse = torch.where(torch.isinf(prefix_lse), torch.full_like(prefix_lse, -math.inf), prefix_lse)
+    s_lse = torch.where(torch.isinf(suffix_lse), torch.full_like(suffix_lse, -math.inf), suffix_lse)
+    mx = torch.maximum(p_lse, s_lse)
+    dead = torch.isinf(mx)
+    safe = torch.where(dead, torch.zeros_like(mx), mx)
+    p_se = torch.exp(p_lse - safe)
+    s_se = torch.exp(s_lse - safe)
+    tot = p_se + s_se
+    ps = (p_se / tot).transpose(0, 1).unsqueeze(-1)  # [T, H, 1]
+    ss = (s_se / tot).transpose(0, 1).unsqueeze(-1)
+    out = prefix_output.float() * ps + suffix_output.float() * ss
+    dead_th = dead.transpose(0, 1).unsqueeze(-1)
+    out = torch.where(dead_th, prefix_output.float(), out).to(prefix_output.dtype)
+    lse = torch.where(dead, mx, torch.log(tot) + safe)
+    return out, lse
+
+
+def copy_blocks(key_caches, value_caches, block_mapping) -> None:
+    """csrc/cache_kernels.cu:73-171: block src -> block dst in every layer's K and V cache."""
+    for src, dst in block_mapping.tolist():
+        for kc, vc in zip(key_caches, value_caches):
+            kc[dst].copy_(kc[src])
+            vc[dst].copy_(vc[src])
+
+
+def swap_blocks(src, dst, block_mapping) -> None:
+    """csrc/cache_kernels.cu:26-69: whole-block copies between two caches."""
+    for s, d in block_mapping.tolist():
+        dst[d].copy_(src[s])

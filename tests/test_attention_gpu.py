@@ -257,3 +257,33 @@ def test_generic_and_tensor_core_kernels_agree():
     w.query, w.key_cache, w.value_cache = q128, kc, vc
     out128 = W.run_attention(w, version="v2")
     torch.testing.assert_close(out128[:, :, :120].float(), out120.float(), atol=2e-4, rtol=1e-2)
+
+
+@pytest.mark.parametrize("version", ["v1", "v2"])
+@pytest.mark.parametrize("step", [0, 2, -1])
+def test_block_sparse_pattern(version, step, ref_cuda_ops):
+    """Block-sparse arguments of the reference signature (local + strided blocks)."""
+    w = W.small(DEV, seed=12, num_seqs=5, num_heads=8, num_kv_heads=2, max_len=1900, num_blocks=700)
+    w.query.mul_(10.0)
+    bs = (1, 2, 4, 64, step)  # tp_rank, local_blocks, vert_stride, blocksparse_block_size, sliding step
+    out = torch.empty_like(w.query)
+    tail = (w.query, w.key_cache, w.value_cache, w.num_kv_heads, w.scale, w.block_tables, w.seq_lens,
+            w.block_size, w.max_seq_len, None, "auto", w.k_scale, w.v_scale) + bs
+    if version == "v1":
+        ops.paged_attention_v1(out, *tail)
+    else:
+        e, m, t = w.scratch()
+        ops.paged_attention_v2(out, e, m, t, *tail)
+    want = O.paged_attention(_cpu(w.query), _cpu(w.key_cache), _cpu(w.value_cache), w.num_kv_heads, w.scale,
+                             _cpu(w.block_tables), _cpu(w.seq_lens), mode="f64", blocksparse=bs)
+    torch.testing.assert_close(out.cpu().double(), want, atol=1e-2, rtol=1e-2)
+    dense = W.run_attention(w, version=version)
+    assert (out.float() - dense.float()).abs().max() > 1e-3  # the pattern really removes tokens
+    if ref_cuda_ops is not None:
+        r = torch.empty_like(w.query)
+        if version == "v1":
+            ref_cuda_ops[0].paged_attention_v1(r, *tail)
+        else:
+            e, m, t = w.scratch()
+            ref_cuda_ops[0].paged_attention_v2(r, e, m, t, *tail)
+        torch.testing.assert_close(out.float(), r.float(), atol=1e-2, rtol=1e-2)

@@ -56,7 +56,7 @@ def _attn(**kw):
     (dict(q_dtype=7), "Unsupported input type"),
     (dict(kv_dtype=9), "Unsupported data type of kv cache"),
     (dict(num_heads=7), "not a multiple"),
-    (dict(blocksparse_vert_stride=2), "block-sparse"),
+    (dict(blocksparse_vert_stride=2, blocksparse_block_size=24), "blocksparse_block_size"),
     (dict(), "null tensor pointer"),
 ])
 def test_attention_argument_errors_are_reported_not_thrown(kw, msg):

@@ -123,3 +123,27 @@ def convert_fp8(
     output: torch.Tensor, input: torch.Tensor, scale: float = 1.0, kv_dtype: str = "fp8"
 ) -> None:
     _cache_ops.convert_fp8(output, input, scale, kv_dtype)
+
+
+def merge_attn_states(
+    output: torch.Tensor,
+    prefix_output: torch.Tensor,
+    prefix_lse: torch.Tensor,
+    suffix_output: torch.Tensor,
+    suffix_lse: torch.Tensor,
+    output_lse: torch.Tensor | None = None,
+) -> None:
+    """Same argument order as the reference wrapper (vllm/_custom_ops.py ``merge_attn_states``)."""
+    _ops.merge_attn_states(output, output_lse, prefix_output, prefix_lse, suffix_output, suffix_lse)
+
+
+def copy_blocks(
+    key_caches: list[torch.Tensor],
+    value_caches: list[torch.Tensor],
+    block_mapping: torch.Tensor,
+) -> None:
+    _cache_ops.copy_blocks(key_caches, value_caches, block_mapping)
+
+
+def swap_blocks(src: torch.Tensor, dst: torch.Tensor, block_mapping: torch.Tensor) -> None:
+    _cache_ops.swap_blocks(src, dst, block_mapping)

@@ -24,6 +24,9 @@ EXPORTS = (
     "b200pa_reshape_and_cache",
     "b200pa_reshape_and_cache_flash",
     "b200pa_convert_fp8",
+    "b200pa_merge_attn_states",
+    "b200pa_copy_blocks",
+    "b200pa_swap_blocks",
     "b200pa_last_error",
     "b200pa_version",
     "b200pa_device_status",

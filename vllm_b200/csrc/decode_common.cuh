@@ -42,6 +42,13 @@ struct DecodeParams {
   int nstages;
   int use_table;       // 1: per-sequence partition prefix table in shared memory
   float scale;
+  // block-sparse attention of the reference signature (generic kernel only); enabled when
+  // bs_vert_stride > 1 (attention_kernels.cuh:204-251)
+  int tp_rank;
+  int bs_local_blocks;
+  int bs_vert_stride;
+  int bs_block_size;
+  int bs_head_sliding_step;
 };
 
 // ------------------------------------------------------------------ PTX wrappers

@@ -6,6 +6,7 @@
 // reference.
 #include <algorithm>
 #include <atomic>
+#include <cfloat>
 #include <cstdlib>
 #include <iterator>
 
@@ -99,6 +100,21 @@ pa_generic_kernel(const DecodeParams p, int head_size, int x) {
   const float vo = KV == kCache16 ? 1.f : *p.v_scale;
   const float qk_scale = p.scale * kLog2e * kq;
   const float slope = p.alibi ? p.alibi[head] * kLog2e : 0.f;
+  // block-sparse pattern: a KV block is attended when it is "local" (among the last
+  // bs_local_blocks sparse blocks of the sequence) or "remote" (every bs_vert_stride-th,
+  // shifted per head); attention_kernels.cuh:204-251
+  const bool sparse = p.bs_vert_stride > 1;
+  const int q_bs_block = sparse ? (len - 1) / p.bs_block_size : 0;
+  const int bs_offset =
+      !sparse ? 0
+              : (p.bs_head_sliding_step >= 0
+                     ? (p.tp_rank * p.num_heads + head) * p.bs_head_sliding_step + 1
+                     : (p.tp_rank * p.num_kv_heads + kvh) * (-p.bs_head_sliding_step) + 1);
+  auto attended = [&](int tok) -> bool {
+    if (!sparse) return true;
+    const int kb = (tok / B) * B / p.bs_block_size;
+    return ((kb + bs_offset) % p.bs_vert_stride == 0) || (kb > q_bs_block - p.bs_local_blocks);
+  };
 
   const QT* q = static_cast<const QT*>(p.q) + int64_t(seq) * p.q_stride + int64_t(head) * head_size;
   for (int d = lane; d < head_size; d += 32) sq[d] = to_f32(q[d]);
@@ -128,6 +144,7 @@ pa_generic_kernel(const DecodeParams p, int head_size, int x) {
       }
       float s = dot * qk_scale;
       if (p.alibi) s += slope * float(tok - len + 1);
+      if (!attended(tok)) s = -FLT_MAX;  // skipped block: no weight, as in the reference
       sl[i] = s;
       lmax = fmaxf(lmax, s);
     }
@@ -138,7 +155,7 @@ pa_generic_kernel(const DecodeParams p, int head_size, int x) {
     float lsum = 0.f;
     for (int i = lane; i < n; i += 32) {
       const float pv = exp2f(sl[i] - m_new);
-      sl[i] = pv;
+      sl[i] = attended(ts + i) ? pv : 0.f;  // skipped blocks never reach the P.V product
       lsum += pv;
     }
 #pragma unroll
@@ -328,11 +345,6 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
   B200PA_CHECK_ARG(a->num_heads % a->num_kv_heads == 0,
                    "num_heads %d is not a multiple of num_kv_heads %d", a->num_heads,
                    a->num_kv_heads);
-  if (a->blocksparse_vert_stride > 1) {
-    set_error("block-sparse paged attention (blocksparse_vert_stride=%d) is not supported",
-              a->blocksparse_vert_stride);
-    return B200PA_EUNSUPPORTED;
-  }
   // same dispatch tables as the reference launchers (paged_attention_v1.cu:90-158)
   static const int kHeadSizes[] = {32, 64, 80, 96, 112, 120, 128, 192, 256};
   bool head_ok = false;
@@ -344,6 +356,13 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
   if (a->block_size != 8 && a->block_size != 16 && a->block_size != 32) {
     set_error("Unsupported block size: %d", a->block_size);
     return B200PA_EUNSUPPORTED;
+  }
+  const bool sparse = a->blocksparse_vert_stride > 1;
+  if (sparse) {
+    B200PA_CHECK_ARG(a->blocksparse_block_size > 0 &&
+                         a->blocksparse_block_size % a->block_size == 0,
+                     "blocksparse_block_size=%d needs to be a positive multiple of block_size=%d",
+                     a->blocksparse_block_size, a->block_size);
   }
   if (a->q_dtype != B200PA_F32 && a->q_dtype != B200PA_F16 && a->q_dtype != B200PA_BF16) {
     set_error("Unsupported input type of kv cache: %d", a->q_dtype);
@@ -397,13 +416,20 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
   p.part_tokens = kPartitionTokens;
   p.group = a->num_heads / a->num_kv_heads;
   p.scale = a->scale;
+  p.tp_rank = a->tp_rank;
+  p.bs_local_blocks = a->blocksparse_local_blocks;
+  p.bs_vert_stride = a->blocksparse_vert_stride;
+  p.bs_block_size = a->blocksparse_block_size;
+  p.bs_head_sliding_step = a->blocksparse_head_sliding_step;
 
   // ---- can the tensor-core kernel take it?
   const int es = a->kv_dtype == B200PA_KV_AUTO ? 2 : 1;
   auto aligned = [](const void* ptr, uintptr_t n) { return reinterpret_cast<uintptr_t>(ptr) % n == 0; };
   const int gp = p.group <= 8 ? 1 : 2;
   DecodeKernelInfo ki{nullptr, 0};
-  bool fast = !force_generic() && a->q_dtype != B200PA_F32 &&
+  // block-sparse attention (unused by any in-tree caller of the reference) runs on the
+  // generic kernel only
+  bool fast = !force_generic() && !sparse && a->q_dtype != B200PA_F32 &&
               (a->block_size == 16 || a->block_size == 32) && a->head_size % 16 == 0 &&
               aligned(a->key_cache, 16) && aligned(a->value_cache, 16) && aligned(a->query, 16) &&
               aligned(a->out, 16) && (!split || aligned(a->tmp_out, 16)) &&

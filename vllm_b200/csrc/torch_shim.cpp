@@ -18,6 +18,7 @@
 
 #include <optional>
 #include <string>
+#include <vector>
 
 #include "../../include/b200pa.h"
 
@@ -276,6 +277,106 @@ void convert_fp8(torch::Tensor& dst_cache, torch::Tensor& src_cache, const doubl
                               at::cuda::getCurrentCUDAStream().stream()));
 }
 
+void merge_attn_states(torch::Tensor& output, std::optional<torch::Tensor> output_lse,
+                       const torch::Tensor& prefix_output, const torch::Tensor& prefix_lse,
+                       const torch::Tensor& suffix_output, const torch::Tensor& suffix_lse) {
+  check_cuda(output, "output");
+  TORCH_CHECK(output.dim() == 3, "output must be [num_tokens, num_heads, head_size]");
+  const int dt = [&]() -> int {
+    switch (output.scalar_type()) {
+      case at::ScalarType::Float: return B200PA_F32;
+      case at::ScalarType::Half: return B200PA_F16;
+      case at::ScalarType::BFloat16: return B200PA_BF16;
+      default: TORCH_CHECK(false, "Unsupported data type of O: ", output.scalar_type());
+    }
+    return -1;
+  }();
+  const int64_t head_size = output.size(2);
+  TORCH_CHECK(output.stride(-2) == head_size && output.stride(-1) == 1,
+              "output heads must be contiguous");
+  TORCH_CHECK(prefix_output.stride(-2) == head_size && prefix_output.stride(-1) == 1,
+              "prefix_output heads must be contiguous");
+  TORCH_CHECK(suffix_output.stride(-2) == head_size && suffix_output.stride(-1) == 1,
+              "suffix_output heads must be contiguous");
+  TORCH_CHECK(output.is_contiguous() && prefix_output.is_contiguous() &&
+                  suffix_output.is_contiguous() && prefix_lse.is_contiguous() &&
+                  suffix_lse.is_contiguous(),
+              "merge_attn_states needs contiguous tensors");
+  TORCH_CHECK(prefix_output.scalar_type() == output.scalar_type() &&
+                  suffix_output.scalar_type() == output.scalar_type(),
+              "prefix/suffix/output dtypes differ");
+  TORCH_CHECK(prefix_lse.scalar_type() == at::ScalarType::Float &&
+                  suffix_lse.scalar_type() == at::ScalarType::Float,
+              "lse tensors must be float32");
+  float* olse = nullptr;
+  if (output_lse.has_value()) {
+    TORCH_CHECK(output_lse->scalar_type() == at::ScalarType::Float && output_lse->is_contiguous(),
+                "output_lse must be a contiguous float32 tensor");
+    olse = output_lse->data_ptr<float>();
+  }
+  const at::cuda::OptionalCUDAGuard device_guard(device_of(output));
+  check_rc(b200pa_merge_attn_states(output.data_ptr(), olse, prefix_output.data_ptr(),
+                                    prefix_lse.data_ptr<float>(), suffix_output.data_ptr(),
+                                    suffix_lse.data_ptr<float>(), output.size(0),
+                                    static_cast<int32_t>(output.size(1)),
+                                    static_cast<int32_t>(head_size), dt,
+                                    at::cuda::getCurrentCUDAStream().stream()));
+}
+
+void copy_blocks(std::vector<torch::Tensor> const& key_caches,
+                 std::vector<torch::Tensor> const& value_caches,
+                 const torch::Tensor& block_mapping) {
+  const size_t num_layers = key_caches.size();
+  TORCH_CHECK(num_layers == value_caches.size());
+  if (num_layers == 0) return;
+  TORCH_CHECK(key_caches[0].is_cuda());
+  TORCH_CHECK(block_mapping.is_cuda() && block_mapping.scalar_type() == at::ScalarType::Long &&
+                  block_mapping.is_contiguous() && block_mapping.dim() == 2 &&
+                  block_mapping.size(1) == 2,
+              "block_mapping must be a contiguous int64 CUDA tensor of shape [num_pairs, 2]");
+  std::vector<void*> kp(num_layers), vp(num_layers);
+  for (size_t i = 0; i < num_layers; ++i) {
+    kp[i] = key_caches[i].data_ptr();
+    vp[i] = value_caches[i].data_ptr();
+  }
+  const int64_t block_bytes = key_caches[0][0].numel() * key_caches[0].element_size();
+  const at::cuda::OptionalCUDAGuard device_guard(key_caches[0].device());
+  check_rc(b200pa_copy_blocks(kp.data(), vp.data(), static_cast<int32_t>(num_layers),
+                              block_mapping.data_ptr<int64_t>(), block_mapping.size(0),
+                              block_bytes, at::cuda::getCurrentCUDAStream().stream()));
+}
+
+void swap_blocks(torch::Tensor& src, torch::Tensor& dst, const torch::Tensor& block_mapping) {
+  const bool sc = src.is_cuda(), dc = dst.is_cuda();
+  if (sc && dc) {
+    TORCH_CHECK(src.device() == dst.device(), "src and dst must be on the same GPU");
+  } else {
+    TORCH_CHECK((sc && dst.is_cpu()) || (src.is_cpu() && dc), "Invalid device combination");
+  }
+  TORCH_CHECK(block_mapping.device().is_cpu(), "block_mapping must be on CPU");
+  TORCH_CHECK(block_mapping.scalar_type() == at::ScalarType::Long && block_mapping.dim() == 2 &&
+                  block_mapping.size(1) == 2,
+              "block_mapping must be an int64 tensor of shape [num_pairs, 2]");
+  const torch::Tensor bm = block_mapping.contiguous();
+  // the stride, not numel, so that padded blocks are copied whole (as the reference does)
+  const int64_t block_bytes = src.element_size() * src.stride(0);
+  const at::cuda::OptionalCUDAGuard device_guard(sc ? src.device() : dst.device());
+  check_rc(b200pa_swap_blocks(src.data_ptr(), dst.data_ptr(), bm.data_ptr<int64_t>(), bm.size(0),
+                              block_bytes, at::cuda::getCurrentCUDAStream().stream()));
+}
+
+constexpr const char* kMergeSchema =
+    "merge_attn_states("
+    "    Tensor! output,"
+    "    Tensor!? output_lse,"
+    "    Tensor prefix_output,"
+    "    Tensor prefix_lse,"
+    "    Tensor suffix_output,"
+    "    Tensor suffix_lse) -> ()";
+constexpr const char* kSwapSchema = "swap_blocks(Tensor src, Tensor! dst, Tensor block_mapping) -> ()";
+constexpr const char* kCopySchema =
+    "copy_blocks(Tensor(a!)[] key_caches, Tensor[](b!) value_caches, "
+    "Tensor block_mapping) -> ()";
 constexpr const char* kV1Schema =
     "paged_attention_v1("
     "    Tensor! out, Tensor query, Tensor key_cache,"
@@ -325,9 +426,15 @@ TORCH_LIBRARY(_C_b200, ops) {
   ops.impl("paged_attention_v1", torch::kCUDA, &paged_attention_v1);
   ops.def(kV2Schema);
   ops.impl("paged_attention_v2", torch::kCUDA, &paged_attention_v2);
+  ops.def(kMergeSchema);
+  ops.impl("merge_attn_states", torch::kCUDA, &merge_attn_states);
 }
 
 TORCH_LIBRARY(_C_b200_cache_ops, cache_ops) {
+  cache_ops.def(kSwapSchema);
+  cache_ops.impl("swap_blocks", torch::kCUDA, &swap_blocks);
+  cache_ops.def(kCopySchema);
+  cache_ops.impl("copy_blocks", torch::kCUDA, &copy_blocks);
   cache_ops.def(kReshapeSchema);
   cache_ops.impl("reshape_and_cache", torch::kCUDA, &reshape_and_cache);
   cache_ops.def(kReshapeFlashSchema);
@@ -346,6 +453,10 @@ TORCH_LIBRARY_FRAGMENT(_C, ops) {
     ops.def(kV2Schema);
     ops.impl("paged_attention_v2", torch::kCUDA, &paged_attention_v2);
   }
+  if (!op_exists("_C::merge_attn_states")) {
+    ops.def(kMergeSchema);
+    ops.impl("merge_attn_states", torch::kCUDA, &merge_attn_states);
+  }
 }
 
 TORCH_LIBRARY_FRAGMENT(_C_cache_ops, cache_ops) {
@@ -356,6 +467,14 @@ TORCH_LIBRARY_FRAGMENT(_C_cache_ops, cache_ops) {
   if (!op_exists("_C_cache_ops::reshape_and_cache_flash")) {
     cache_ops.def(kReshapeFlashSchema);
     cache_ops.impl("reshape_and_cache_flash", torch::kCUDA, &reshape_and_cache_flash);
+  }
+  if (!op_exists("_C_cache_ops::swap_blocks")) {
+    cache_ops.def(kSwapSchema);
+    cache_ops.impl("swap_blocks", torch::kCUDA, &swap_blocks);
+  }
+  if (!op_exists("_C_cache_ops::copy_blocks")) {
+    cache_ops.def(kCopySchema);
+    cache_ops.impl("copy_blocks", torch::kCUDA, &copy_blocks);
   }
   if (!op_exists("_C_cache_ops::convert_fp8")) {
     cache_ops.def(kConvertSchema);
