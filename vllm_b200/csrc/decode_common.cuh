@@ -39,7 +39,8 @@ struct DecodeParams {
   int part_tokens;     // tokens per partition (512 for v2; v1 may split finer into library scratch)
   int group;           // query heads per kv head
   int head_groups;     // ceil(group / heads per item)
-  int nstages;
+  int nstages;         // ring slots per warp
+  int split_kv;        // 1: K and V pages in separate slots; 0: one slot per block (K + V)
   int use_table;       // 1: per-sequence partition prefix table in shared memory
   float scale;
   // block-sparse attention of the reference signature (generic kernel only); enabled when

@@ -2,7 +2,7 @@
 #include "decode_inst.cuh"
 
 namespace b200pa {
-DecodeKernelInfo find_decode_d128(int q_dtype, int kv_dtype, int gp) {
-  return find_decode_for<128>(q_dtype, kv_dtype, gp);
+DecodeKernelInfo find_decode_d128(int q_dtype, int kv_dtype, int gp, int nt) {
+  return find_decode_for<128>(q_dtype, kv_dtype, gp, nt);
 }
 }  // namespace b200pa

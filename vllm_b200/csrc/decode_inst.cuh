@@ -22,10 +22,10 @@ constexpr int decode_max_warps() {
   return (D * GP <= 128) ? 16 : 8;
 }
 
-template <typename QT, int KV, int D, int GP, int CVT = 2>
+template <typename QT, int KV, int D, int GP, int NT>
 cudaError_t decode_launch(const DecodeParams& p, int grid, int threads, size_t smem,
                           cudaStream_t stream) {
-  auto kern = pa_decode_kernel<QT, KV, D, GP, decode_max_warps<KV, D, GP>(), CVT>;
+  auto kern = pa_decode_kernel<QT, KV, D, GP, NT, decode_max_warps<KV, D, GP>()>;
   // opt in to large dynamic shared memory once per device
   static bool done[64] = {};
   int dev = 0;
@@ -48,38 +48,45 @@ cudaError_t decode_launch(const DecodeParams& p, int grid, int threads, size_t s
   return cudaGetLastError();
 }
 
+template <typename QT, int KV, int D, int GP>
+DecodeKernelInfo pick_nt(int nt) {
+  if (nt == 1) return {decode_launch<QT, KV, D, GP, 1>, decode_max_warps<KV, D, GP>()};
+  return {decode_launch<QT, KV, D, GP, 2>, decode_max_warps<KV, D, GP>()};
+}
+
 template <typename QT, int KV, int D>
-DecodeKernelInfo pick_gp(int gp) {
-  if (gp == 1) return {decode_launch<QT, KV, D, 1>, decode_max_warps<KV, D, 1>()};
-  return {decode_launch<QT, KV, D, 2>, decode_max_warps<KV, D, 2>()};
+DecodeKernelInfo pick_gp(int gp, int nt) {
+  if (gp == 1) return pick_nt<QT, KV, D, 1>(nt);
+  return pick_nt<QT, KV, D, 2>(nt);
 }
 
 template <typename QT, int D>
-DecodeKernelInfo pick_kv(int kv_dtype, int gp) {
+DecodeKernelInfo pick_kv(int kv_dtype, int gp, int nt) {
   switch (kv_dtype) {
-    case B200PA_KV_AUTO: return pick_gp<QT, kCache16, D>(gp);
-    case B200PA_KV_FP8_E4M3: return pick_gp<QT, kCacheE4M3, D>(gp);
-    case B200PA_KV_FP8_E5M2: return pick_gp<QT, kCacheE5M2, D>(gp);
+    case B200PA_KV_AUTO: return pick_gp<QT, kCache16, D>(gp, nt);
+    case B200PA_KV_FP8_E4M3: return pick_gp<QT, kCacheE4M3, D>(gp, nt);
+    case B200PA_KV_FP8_E5M2: return pick_gp<QT, kCacheE5M2, D>(gp, nt);
   }
   return {nullptr, 0};
 }
 
+// gp: 8-head n-tiles per work item (1 or 2); nt: 16-token tiles per cache block (1 or 2).
 template <int D>
-DecodeKernelInfo find_decode_for(int q_dtype, int kv_dtype, int gp) {
-  if (gp != 1 && gp != 2) return {nullptr, 0};
-  if (q_dtype == B200PA_BF16) return pick_kv<__nv_bfloat16, D>(kv_dtype, gp);
-  if (q_dtype == B200PA_F16) return pick_kv<__half, D>(kv_dtype, gp);
+DecodeKernelInfo find_decode_for(int q_dtype, int kv_dtype, int gp, int nt) {
+  if ((gp != 1 && gp != 2) || (nt != 1 && nt != 2)) return {nullptr, 0};
+  if (q_dtype == B200PA_BF16) return pick_kv<__nv_bfloat16, D>(kv_dtype, gp, nt);
+  if (q_dtype == B200PA_F16) return pick_kv<__half, D>(kv_dtype, gp, nt);
   return {nullptr, 0};
 }
 
 // One finder per translation unit (defined in decode_d*.cu).
-DecodeKernelInfo find_decode_d32(int q_dtype, int kv_dtype, int gp);
-DecodeKernelInfo find_decode_d64(int q_dtype, int kv_dtype, int gp);
-DecodeKernelInfo find_decode_d80(int q_dtype, int kv_dtype, int gp);
-DecodeKernelInfo find_decode_d96(int q_dtype, int kv_dtype, int gp);
-DecodeKernelInfo find_decode_d112(int q_dtype, int kv_dtype, int gp);
-DecodeKernelInfo find_decode_d128(int q_dtype, int kv_dtype, int gp);
-DecodeKernelInfo find_decode_d192(int q_dtype, int kv_dtype, int gp);
-DecodeKernelInfo find_decode_d256(int q_dtype, int kv_dtype, int gp);
+DecodeKernelInfo find_decode_d32(int q_dtype, int kv_dtype, int gp, int nt);
+DecodeKernelInfo find_decode_d64(int q_dtype, int kv_dtype, int gp, int nt);
+DecodeKernelInfo find_decode_d80(int q_dtype, int kv_dtype, int gp, int nt);
+DecodeKernelInfo find_decode_d96(int q_dtype, int kv_dtype, int gp, int nt);
+DecodeKernelInfo find_decode_d112(int q_dtype, int kv_dtype, int gp, int nt);
+DecodeKernelInfo find_decode_d128(int q_dtype, int kv_dtype, int gp, int nt);
+DecodeKernelInfo find_decode_d192(int q_dtype, int kv_dtype, int gp, int nt);
+DecodeKernelInfo find_decode_d256(int q_dtype, int kv_dtype, int gp, int nt);
 
 }  // namespace b200pa

@@ -68,7 +68,7 @@ __device__ __forceinline__ int load_bt(const DecodeParams& p, const WorkItem& it
   return __ldg(p.block_tables + int64_t(it.seq) * p.max_blocks_per_seq + it.first_page + pg);
 }
 
-template <typename QT, int KV, int D, int GP, int MAXW, int CVT = 2>
+template <typename QT, int KV, int D, int GP, int NT, int MAXW, int CVT = 2>
 __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodeParams p) {
   using TR = DecodeTraits<QT, KV, D, GP>;
   constexpr bool kFp8 = TR::kFp8;
@@ -89,21 +89,25 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
   const int nwarps = blockDim.x >> 5;
   const int g = lane >> 2;  // fragment row group
   const int c = lane & 3;   // fragment column pair
-  const int B = p.block_size;
-  const int NS = p.nstages;
+  constexpr int B = 16 * NT;  // tokens per cache block (16 or 32)
+  constexpr uint32_t page_bytes = uint32_t(D) * B * (KV != kCache16 ? 1 : 2);
+  const int NSLOT = p.nstages;  // ring slots of this warp
+  // split_kv: a slot holds one K page or one V page, each with its own barrier (finer
+  // prefetch granularity, pays off for pages >= 4 KiB); else a slot holds the K and the V
+  // page of one block behind one barrier (half the barrier traffic, better for small pages)
+  const bool split_kv = p.split_kv != 0;
+  const uint32_t slot_bytes = split_kv ? page_bytes : 2 * page_bytes;
   const int PT = p.part_tokens;  // tokens per split-KV partition (a multiple of the block size)
-  const uint32_t page_bytes = uint32_t(D) * B * ES;
-  const uint32_t stage_bytes = 2 * page_bytes;
 
   // ---- shared memory carve-up: [partition prefix table][mbarriers][stages]
   int* cum = reinterpret_cast<int*>(smem_raw);
   const int table_ints = p.use_table ? ((p.num_seqs + 1 + 3) & ~3) : 0;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + size_t(table_ints) * 4);
-  const uint32_t bars_bytes = (uint32_t(nwarps) * NS * 8 + 127u) & ~127u;
-  unsigned char* stages = smem_raw + size_t(table_ints) * 4 + bars_bytes;
+  const uint32_t bars_bytes = (uint32_t(nwarps) * NSLOT * 8 + 127u) & ~127u;
+  unsigned char* slots = smem_raw + size_t(table_ints) * 4 + bars_bytes;
   // the dynamic buffer is 128-byte aligned and table_ints*4 is a multiple of 16
-  const uint32_t my_stage0 = smem_u32(stages) + uint32_t(warp) * NS * stage_bytes;
-  const uint32_t my_bar0 = smem_u32(bars) + uint32_t(warp) * NS * 8;
+  const uint32_t my_slot0 = smem_u32(slots) + uint32_t(warp) * NSLOT * slot_bytes;
+  const uint32_t my_bar0 = smem_u32(bars) + uint32_t(warp) * NSLOT * 8;
 
   // ---- set-up: prefix table of partitions per sequence (exclusive scan)
   if (p.use_table) {
@@ -136,7 +140,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
     if (threadIdx.x == blockDim.x - 1) cum[S] = run;
   }
   if (lane == 0) {
-    for (int s = 0; s < NS; ++s) mbar_init(my_bar0 + s * 8, 1);
+    for (int s = 0; s < NSLOT; ++s) mbar_init(my_bar0 + s * 8, 1);
     fence_barrier_init();
   }
   __syncthreads();
@@ -193,42 +197,56 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
   WorkItem nxt = decode(fetch());
   unsigned nn_raw = fetch();
 
-  // ---- producer state
-  int prod_sel = 0;  // 0: producing pages of `cur`, 1: of `nxt`
+  // ---- producer state.  The ring is filled in the order K(page 0), V(page 0), K(page 1), ...
+  int prod_sel = 0;   // 0: producing pages of `cur`, 1: of `nxt`
   int prod_pg = 0;
-  int prod_stage = 0;
+  int prod_half = 0;  // 0: the K page is next, 1: the V page of the same block
+  int prod_blk = 0;
+  int prod_slot = 0;
   int inflight = 0;
-  int cons_stage = 0;
+  int cons_slot = 0;
   uint32_t cons_phase = 0;
 
   auto produce_one = [&]() -> bool {
-    if (prod_sel == 0 && prod_pg >= cur.npages) {
-      prod_sel = 1;
-      prod_pg = 0;
+    if (prod_half == 0) {
+      if (prod_sel == 0 && prod_pg >= cur.npages) {
+        prod_sel = 1;
+        prod_pg = 0;
+      }
+      if (prod_sel == 1 && (!nxt.valid || prod_pg >= nxt.npages)) return false;
+      WorkItem& it = prod_sel ? nxt : cur;
+      const int win = prod_pg >> 5;
+      if (win != it.win) {
+        it.win = win;
+        it.bt = load_bt(p, it, win, lane);
+      }
+      prod_blk = __shfl_sync(0xffffffffu, it.bt, prod_pg & 31);
     }
-    if (prod_sel == 1 && (!nxt.valid || prod_pg >= nxt.npages)) return false;
-    WorkItem& it = prod_sel ? nxt : cur;
-    const int win = prod_pg >> 5;
-    if (win != it.win) {
-      it.win = win;
-      it.bt = load_bt(p, it, win, lane);
-    }
-    const int blk = __shfl_sync(0xffffffffu, it.bt, prod_pg & 31);
     if (lane == 0) {
-      const int64_t off = (int64_t(blk) * p.kv_block_stride + int64_t(it.kvh) * p.kv_head_stride) * ES;
-      const uint32_t bar = my_bar0 + prod_stage * 8;
-      const uint32_t dst = my_stage0 + prod_stage * stage_bytes;
-      mbar_expect_tx(bar, stage_bytes);
-      bulk_g2s(dst, kc_base + off, page_bytes, bar, policy);
-      bulk_g2s(dst + page_bytes, vc_base + off, page_bytes, bar, policy);
+      const int kvh = prod_sel ? nxt.kvh : cur.kvh;
+      const int64_t off = (int64_t(prod_blk) * p.kv_block_stride + int64_t(kvh) * p.kv_head_stride) * ES;
+      const uint32_t bar = my_bar0 + prod_slot * 8;
+      const uint32_t dst = my_slot0 + prod_slot * slot_bytes;
+      mbar_expect_tx(bar, slot_bytes);
+      if (split_kv) {
+        bulk_g2s(dst, (prod_half ? vc_base : kc_base) + off, page_bytes, bar, policy);
+      } else {
+        bulk_g2s(dst, kc_base + off, page_bytes, bar, policy);
+        bulk_g2s(dst + page_bytes, vc_base + off, page_bytes, bar, policy);
+      }
     }
-    prod_stage = (prod_stage + 1 == NS) ? 0 : prod_stage + 1;
-    ++prod_pg;
+    prod_slot = (prod_slot + 1 == NSLOT) ? 0 : prod_slot + 1;
+    if (split_kv) {
+      if (prod_half) ++prod_pg;
+      prod_half ^= 1;
+    } else {
+      ++prod_pg;
+    }
     ++inflight;
     return true;
   };
 
-  while (inflight < NS && produce_one()) {}
+  while (inflight < NSLOT && produce_one()) {}
 
   // fp8 values come out of fp8x4_to_f16 scaled by 1/kPrescale; fold that and the
   // per-tensor scales into the logit scale and the output scale
@@ -292,108 +310,105 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
     }
 
     for (int pg = 0; pg < cur.npages; ++pg) {
-      const uint32_t bar = my_bar0 + cons_stage * 8;
-      if (!__all_sync(0xffffffffu, mbar_wait(bar, cons_phase))) {
+      const int page_tok0 = (cur.first_page + pg) * B;
+      // tiles of this page that hold at least one valid token (warp-uniform)
+      const int ntiles = min(NT, (cur.tok_end - page_tok0 + 15) >> 4);
+
+      // ================= K half: S^T = K . Q^T for every tile of the page
+      if (!__all_sync(0xffffffffu, mbar_wait(my_bar0 + cons_slot * 8, cons_phase))) {
         if (lane == 0) atomicExch(p.status, kStatusMbarTimeout);
         failed = true;
         break;
       }
-      const uint32_t sk = my_stage0 + cons_stage * stage_bytes;
-      const uint32_t sv = sk + page_bytes;
-      const int page_tok0 = (cur.first_page + pg) * B;
-
-      // zero V columns of tokens past the end of the sequence (stale cache bytes
-      // could be NaN/Inf; the reference zeroes them too, attention_kernels.cuh:415-425)
-      if (page_tok0 + B > cur.tok_end) {
-        const int rem = cur.tok_end - page_tok0;
-        const int w = B - rem;
-        unsigned char* vpage = stages + size_t(warp) * NS * stage_bytes +
-                               size_t(cons_stage) * stage_bytes + page_bytes;
-        for (int idx = lane; idx < D * w; idx += 32) {
-          const int d = idx / w;
-          const int t = rem + idx % w;
-          if constexpr (ES == 1) vpage[d * B + t] = 0;
-          else reinterpret_cast<uint16_t*>(vpage)[d * B + t] = 0;
+      const uint32_t sk = my_slot0 + cons_slot * slot_bytes;
+      float s[NT][GP][4];
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        constexpr int kZero = 0;
+        float s2[GP][4];  // second accumulation chain: halves the dependent-MMA latency
+#pragma unroll
+        for (int nt = 0; nt < GP; ++nt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) s[t][nt][i] = s2[nt][i] = float(kZero);
+        if (t < ntiles) {
+          const int tt = 16 * t;
+          if constexpr (!kFp8) {
+            const uint32_t kaddr =
+                sk + uint32_t(((lane >> 4) * B + tt + ((lane >> 3) & 1) * 8 + (lane & 7)) * 16);
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+              uint32_t a0, a1, a2, a3;
+              ldsm_x4(kaddr + uint32_t(2 * ks * B * 16), a0, a1, a2, a3);
+#pragma unroll
+              for (int nt = 0; nt < GP; ++nt) {
+                if (ks & 1) mma16816<kBf>(s2[nt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
+                else mma16816<kBf>(s[t][nt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
+              }
+            }
+          } else {
+            // A row rho of half h <-> token 4*(rho/2) + 2*h + rho%2
+            const int rho = lane & 7, hsel = (lane >> 3) & 1;
+            const int tok = 4 * (rho >> 1) + 2 * hsel + (rho & 1);
+            const uint32_t kaddr = sk + uint32_t(((lane >> 4) * B + tt + tok) * 16);
+#pragma unroll
+            for (int ks = 0; ks + 1 < KS; ks += 2) {
+              uint32_t r0, r1, r2, r3, a0, a1, a2, a3, b0, b1, b2, b3;
+              ldsm_x4(kaddr + uint32_t(ks * B * 16), r0, r1, r2, r3);
+              fp8x4_to_f16<kE5, kAluK>(r0, a0, a2);
+              fp8x4_to_f16<kE5, kAluK>(r1, a1, a3);
+              fp8x4_to_f16<kE5, kAluK>(r2, b0, b2);
+              fp8x4_to_f16<kE5, kAluK>(r3, b1, b3);
+#pragma unroll
+              for (int nt = 0; nt < GP; ++nt) {
+                mma16816<false>(s[t][nt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
+                mma16816<false>(s2[nt], b0, b1, b2, b3, qf[nt][ks + 1][0], qf[nt][ks + 1][1]);
+              }
+            }
+            if constexpr (KS & 1) {
+              constexpr int ks = KS - 1;
+              uint32_t r0, r1, a0, a1, a2, a3;
+              // lanes 0-15 supply the addresses of the two matrices (lanes 16-31 ignored)
+              ldsm_x2(sk + uint32_t((ks * B + tt + tok) * 16), r0, r1);
+              fp8x4_to_f16<kE5, kAluK>(r0, a0, a2);
+              fp8x4_to_f16<kE5, kAluK>(r1, a1, a3);
+#pragma unroll
+              for (int nt = 0; nt < GP; ++nt)
+                mma16816<false>(s[t][nt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
+            }
+          }
+#pragma unroll
+          for (int nt = 0; nt < GP; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s[t][nt][i] += s2[nt][i];
         }
+      }
+      if (split_kv) {
+        // the K slot is free: refill it while the softmax runs
         __syncwarp();
+        cons_slot = (cons_slot + 1 == NSLOT) ? 0 : cons_slot + 1;
+        if (cons_slot == 0) cons_phase ^= 1;
+        --inflight;
+        produce_one();
       }
 
-      for (int tt = 0; tt < B; tt += 16) {
-        const int tile_tok0 = page_tok0 + tt;
-        if (tile_tok0 >= cur.tok_end) break;
-
-        // ---------------- S^T = K . Q^T
-        float s[GP][4], s2[GP][4];  // two accumulation chains halve the dependent-MMA latency
+      // ================= scale, ALiBi, mask; online softmax over the whole page
+      const bool need_mask = page_tok0 + B > cur.tok_end;
 #pragma unroll
-        for (int nt = 0; nt < GP; ++nt)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) s[nt][i] = s2[nt][i] = 0.f;
-
-        if constexpr (!kFp8) {
-          const uint32_t kaddr =
-              sk + uint32_t((((lane >> 4)) * B + tt + ((lane >> 3) & 1) * 8 + (lane & 7)) * 16);
-#pragma unroll
-          for (int ks = 0; ks < KS; ++ks) {
-            uint32_t a0, a1, a2, a3;
-            ldsm_x4(kaddr + uint32_t(2 * ks * B * 16), a0, a1, a2, a3);
-#pragma unroll
-            for (int nt = 0; nt < GP; ++nt) {
-              if (ks & 1) mma16816<kBf>(s2[nt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
-              else mma16816<kBf>(s[nt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
-            }
-          }
-        } else {
-          // A row rho of half h <-> token 4*(rho/2) + 2*h + rho%2
-          const int rho = lane & 7, hsel = (lane >> 3) & 1;
-          const int tok = 4 * (rho >> 1) + 2 * hsel + (rho & 1);
-          const uint32_t kaddr = sk + uint32_t(((lane >> 4) * B + tt + tok) * 16);
-#pragma unroll
-          for (int ks = 0; ks + 1 < KS; ks += 2) {
-            uint32_t r0, r1, r2, r3, a0, a1, a2, a3, b0, b1, b2, b3;
-            ldsm_x4(kaddr + uint32_t(ks * B * 16), r0, r1, r2, r3);
-            fp8x4_to_f16<kE5, kAluK>(r0, a0, a2);
-            fp8x4_to_f16<kE5, kAluK>(r1, a1, a3);
-            fp8x4_to_f16<kE5, kAluK>(r2, b0, b2);
-            fp8x4_to_f16<kE5, kAluK>(r3, b1, b3);
-#pragma unroll
-            for (int nt = 0; nt < GP; ++nt) {
-              mma16816<false>(s[nt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
-              mma16816<false>(s2[nt], b0, b1, b2, b3, qf[nt][ks + 1][0], qf[nt][ks + 1][1]);
-            }
-          }
-          if constexpr (KS & 1) {
-            constexpr int ks = KS - 1;
-            uint32_t r0, r1, a0, a1, a2, a3;
-            // lanes 0-15 supply the addresses of the two matrices (lanes 16-31 ignored)
-            ldsm_x2(sk + uint32_t((ks * B + tt + tok) * 16), r0, r1);
-            fp8x4_to_f16<kE5, kAluK>(r0, a0, a2);
-            fp8x4_to_f16<kE5, kAluK>(r1, a1, a3);
-#pragma unroll
-            for (int nt = 0; nt < GP; ++nt)
-              mma16816<false>(s[nt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
-          }
-        }
-#pragma unroll
-        for (int nt = 0; nt < GP; ++nt)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) s[nt][i] += s2[nt][i];
-
-        // ---------------- scale, ALiBi, mask
+      for (int t = 0; t < NT; ++t) {
         int tok_lo, tok_hi;  // absolute token of accumulator rows g and g+8
         if constexpr (!kFp8) {
-          tok_lo = tile_tok0 + g;
-          tok_hi = tile_tok0 + g + 8;
+          tok_lo = page_tok0 + 16 * t + g;
+          tok_hi = tok_lo + 8;
         } else {
-          tok_lo = tile_tok0 + 4 * (g >> 1) + (g & 1);
+          tok_lo = page_tok0 + 16 * t + 4 * (g >> 1) + (g & 1);
           tok_hi = tok_lo + 2;
         }
-        const bool need_mask = tile_tok0 + 16 > cur.tok_end;
 #pragma unroll
         for (int nt = 0; nt < GP; ++nt) {
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
-            float v_lo = s[nt][j] * qk_scale;
-            float v_hi = s[nt][2 + j] * qk_scale;
+            float v_lo = s[t][nt][j] * qk_scale;
+            float v_hi = s[t][nt][2 + j] * qk_scale;
             if (p.alibi != nullptr) {
               v_lo += slope[nt][j] * float(tok_lo - seq_len + 1);
               v_hi += slope[nt][j] * float(tok_hi - seq_len + 1);
@@ -402,102 +417,131 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
               if (tok_lo >= cur.tok_end) v_lo = -INFINITY;
               if (tok_hi >= cur.tok_end) v_hi = -INFINITY;
             }
-            s[nt][j] = v_lo;
-            s[nt][2 + j] = v_hi;
+            s[t][nt][j] = v_lo;
+            s[t][nt][2 + j] = v_hi;
           }
         }
+      }
+      float alpha[GP][2];
+      bool rescale = false;
+#pragma unroll
+      for (int nt = 0; nt < GP; ++nt) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          float tmax = fmaxf(s[0][nt][j], s[0][nt][2 + j]);
+#pragma unroll
+          for (int t = 1; t < NT; ++t) tmax = fmaxf(tmax, fmaxf(s[t][nt][j], s[t][nt][2 + j]));
+          tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 4));
+          tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 8));
+          tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 16));
+          const float m_old = m_run[nt][j];
+          const float m_new = fmaxf(m_old, tmax);
+          // m_new is finite here: every processed page holds at least one valid token
+          alpha[nt][j] = fast_exp2(m_old - m_new);
+          rescale |= (m_new != m_old);
+          m_run[nt][j] = m_new;
+          float psum = 0.f;
+#pragma unroll
+          for (int t = 0; t < NT; ++t) {
+            const float p_lo = fast_exp2(s[t][nt][j] - m_new);
+            const float p_hi = fast_exp2(s[t][nt][2 + j] - m_new);
+            psum += p_lo + p_hi;
+            s[t][nt][j] = p_lo;
+            s[t][nt][2 + j] = p_hi;
+          }
+          l_run[nt][j] = l_run[nt][j] * alpha[nt][j] + psum;
+        }
+      }
+      if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+        for (int mt = 0; mt < KS; ++mt)
+#pragma unroll
+          for (int nt = 0; nt < GP; ++nt) {
+            o[mt][nt][0] *= alpha[nt][0];
+            o[mt][nt][1] *= alpha[nt][1];
+            o[mt][nt][2] *= alpha[nt][0];
+            o[mt][nt][3] *= alpha[nt][1];
+          }
+      }
 
-        // ---------------- online softmax (per head; heads 2c, 2c+1 of each n-tile)
-        float alpha[GP][2];
-        bool rescale = false;
-#pragma unroll
-        for (int nt = 0; nt < GP; ++nt) {
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            float tmax = fmaxf(s[nt][j], s[nt][2 + j]);
-            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 4));
-            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 8));
-            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 16));
-            const float m_old = m_run[nt][j];
-            const float m_new = fmaxf(m_old, tmax);
-            // m_new is finite here: every processed tile holds at least one valid token
-            alpha[nt][j] = fast_exp2(m_old - m_new);
-            rescale |= (m_new != m_old);
-            m_run[nt][j] = m_new;
-            const float p_lo = fast_exp2(s[nt][j] - m_new);
-            const float p_hi = fast_exp2(s[nt][2 + j] - m_new);
-            l_run[nt][j] = l_run[nt][j] * alpha[nt][j] + p_lo + p_hi;
-            s[nt][j] = p_lo;
-            s[nt][2 + j] = p_hi;
-          }
+      // ================= V half: O^T += V^T . P^T
+      if (split_kv && !__all_sync(0xffffffffu, mbar_wait(my_bar0 + cons_slot * 8, cons_phase))) {
+        if (lane == 0) atomicExch(p.status, kStatusMbarTimeout);
+        failed = true;
+        break;
+      }
+      const uint32_t sv = my_slot0 + cons_slot * slot_bytes + (split_kv ? 0u : page_bytes);
+      // zero V columns of tokens past the end of the sequence (stale cache bytes
+      // could be NaN/Inf; the reference zeroes them too, attention_kernels.cuh:415-425)
+      if (need_mask) {
+        const int rem = cur.tok_end - page_tok0;
+        const int w = B - rem;
+        unsigned char* vpage = slots + (size_t(warp) * NSLOT + cons_slot) * slot_bytes +
+                               (split_kv ? 0u : page_bytes);
+        for (int idx = lane; idx < D * w; idx += 32) {
+          const int d = idx / w;
+          const int tk = rem + idx % w;
+          if constexpr (ES == 1) vpage[d * B + tk] = 0;
+          else reinterpret_cast<uint16_t*>(vpage)[d * B + tk] = 0;
         }
-        if (__any_sync(0xffffffffu, rescale)) {
+        __syncwarp();
+      }
 #pragma unroll
-          for (int mt = 0; mt < KS; ++mt)
+      for (int t = 0; t < NT; ++t) {
+        if (t < ntiles) {
+          const int tt = 16 * t;
+          uint32_t pf[GP][2];  // P^T as B operand
 #pragma unroll
-            for (int nt = 0; nt < GP; ++nt) {
-              o[mt][nt][0] *= alpha[nt][0];
-              o[mt][nt][1] *= alpha[nt][1];
-              o[mt][nt][2] *= alpha[nt][0];
-              o[mt][nt][3] *= alpha[nt][1];
+          for (int nt = 0; nt < GP; ++nt) {
+            pf[nt][0] = movm_trans(pack2<kBf>(s[t][nt][0], s[t][nt][1]));
+            pf[nt][1] = movm_trans(pack2<kBf>(s[t][nt][2], s[t][nt][3]));
+          }
+          if constexpr (!kFp8) {
+            const uint32_t vaddr =
+                sv + uint32_t(((((lane >> 3) & 1) * 8 + (lane & 7)) * B + tt + (lane >> 4) * 8) * 2);
+#pragma unroll
+            for (int mt = 0; mt < KS; ++mt) {
+              uint32_t a0, a1, a2, a3;
+              ldsm_x4(vaddr + uint32_t(16 * mt * B * 2), a0, a1, a2, a3);
+#pragma unroll
+              for (int nt = 0; nt < GP; ++nt)
+                mma16816<kBf>(o[mt][nt], a0, a1, a2, a3, pf[nt][0], pf[nt][1]);
             }
-        }
-
-        // ---------------- P^T as B operand
-        uint32_t pf[GP][2];
+          } else {
+            const uint32_t vaddr =
+                sv + uint32_t((16 * (lane >> 4) + ((lane >> 3) & 1) * 8 + (lane & 7)) * B + tt);
 #pragma unroll
-        for (int nt = 0; nt < GP; ++nt) {
-          pf[nt][0] = movm_trans(pack2<kBf>(s[nt][0], s[nt][1]));
-          pf[nt][1] = movm_trans(pack2<kBf>(s[nt][2], s[nt][3]));
-        }
-
-        // ---------------- O^T += V^T . P^T
-        if constexpr (!kFp8) {
-          const uint32_t vaddr =
-              sv + uint32_t(((((lane >> 3) & 1) * 8 + (lane & 7)) * B + tt + (lane >> 4) * 8) * 2);
+            for (int mt = 0; mt + 1 < KS; mt += 2) {
+              uint32_t r0, r1, r2, r3, a0, a1, a2, a3, b0, b1, b2, b3;
+              ldsm_x4(vaddr + uint32_t(16 * mt * B), r0, r1, r2, r3);
+              fp8x4_to_f16<kE5, kAluV>(r0, a0, a2);
+              fp8x4_to_f16<kE5, kAluV>(r1, a1, a3);
+              fp8x4_to_f16<kE5, kAluV>(r2, b0, b2);
+              fp8x4_to_f16<kE5, kAluV>(r3, b1, b3);
 #pragma unroll
-          for (int mt = 0; mt < KS; ++mt) {
-            uint32_t a0, a1, a2, a3;
-            ldsm_x4(vaddr + uint32_t(16 * mt * B * 2), a0, a1, a2, a3);
+              for (int nt = 0; nt < GP; ++nt) {
+                mma16816<false>(o[mt][nt], a0, a1, a2, a3, pf[nt][0], pf[nt][1]);
+                mma16816<false>(o[mt + 1][nt], b0, b1, b2, b3, pf[nt][0], pf[nt][1]);
+              }
+            }
+            if constexpr (KS & 1) {
+              constexpr int mt = KS - 1;
+              uint32_t r0, r1, a0, a1, a2, a3;
+              ldsm_x2(sv + uint32_t((16 * mt + ((lane >> 3) & 1) * 8 + (lane & 7)) * B + tt), r0, r1);
+              fp8x4_to_f16<kE5, kAluV>(r0, a0, a2);
+              fp8x4_to_f16<kE5, kAluV>(r1, a1, a3);
 #pragma unroll
-            for (int nt = 0; nt < GP; ++nt)
-              mma16816<kBf>(o[mt][nt], a0, a1, a2, a3, pf[nt][0], pf[nt][1]);
-          }
-        } else {
-          const uint32_t vaddr =
-              sv + uint32_t((16 * (lane >> 4) + ((lane >> 3) & 1) * 8 + (lane & 7)) * B + tt);
-#pragma unroll
-          for (int mt = 0; mt + 1 < KS; mt += 2) {
-            uint32_t r0, r1, r2, r3, a0, a1, a2, a3, b0, b1, b2, b3;
-            ldsm_x4(vaddr + uint32_t(16 * mt * B), r0, r1, r2, r3);
-            fp8x4_to_f16<kE5, kAluV>(r0, a0, a2);
-            fp8x4_to_f16<kE5, kAluV>(r1, a1, a3);
-            fp8x4_to_f16<kE5, kAluV>(r2, b0, b2);
-            fp8x4_to_f16<kE5, kAluV>(r3, b1, b3);
-#pragma unroll
-            for (int nt = 0; nt < GP; ++nt) {
-              mma16816<false>(o[mt][nt], a0, a1, a2, a3, pf[nt][0], pf[nt][1]);
-              mma16816<false>(o[mt + 1][nt], b0, b1, b2, b3, pf[nt][0], pf[nt][1]);
+              for (int nt = 0; nt < GP; ++nt)
+                mma16816<false>(o[mt][nt], a0, a1, a2, a3, pf[nt][0], pf[nt][1]);
             }
           }
-          if constexpr (KS & 1) {
-            constexpr int mt = KS - 1;
-            uint32_t r0, r1, a0, a1, a2, a3;
-            ldsm_x2(sv + uint32_t((16 * mt + ((lane >> 3) & 1) * 8 + (lane & 7)) * B + tt), r0, r1);
-            fp8x4_to_f16<kE5, kAluV>(r0, a0, a2);
-            fp8x4_to_f16<kE5, kAluV>(r1, a1, a3);
-#pragma unroll
-            for (int nt = 0; nt < GP; ++nt)
-              mma16816<false>(o[mt][nt], a0, a1, a2, a3, pf[nt][0], pf[nt][1]);
-          }
         }
-      }  // tiles of the page
-
-      // ---- release the stage and refill it
+      }
+      // ---- release the V slot and refill it
       __syncwarp();
-      if (page_tok0 + B > cur.tok_end) fence_proxy_async();  // generic writes above vs. the next bulk copy
-      cons_stage = (cons_stage + 1 == NS) ? 0 : cons_stage + 1;
-      if (cons_stage == 0) cons_phase ^= 1;
+      if (need_mask) fence_proxy_async();  // generic writes above vs. the next bulk copy
+      cons_slot = (cons_slot + 1 == NSLOT) ? 0 : cons_slot + 1;
+      if (cons_slot == 0) cons_phase ^= 1;
       --inflight;
       produce_one();
     }  // pages
@@ -622,17 +666,16 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
     nxt = decode(nn_raw);
     nn_raw = fetch();
     if (prod_sel == 1) prod_sel = 0; else prod_pg = 0;
-    while (inflight < NS && produce_one()) {}
+    while (inflight < NSLOT && produce_one()) {}
   }
 
   if (failed) {
     // give copies already in flight a bounded chance to land before the CTA's
     // shared memory is released
     for (int i = 0; i < inflight; ++i) {
-      const uint32_t bar = my_bar0 + cons_stage * 8;
-      mbar_wait(bar, cons_phase);
-      cons_stage = (cons_stage + 1 == NS) ? 0 : cons_stage + 1;
-      if (cons_stage == 0) cons_phase ^= 1;
+      mbar_wait(my_bar0 + cons_slot * 8, cons_phase);
+      cons_slot = (cons_slot + 1 == NSLOT) ? 0 : cons_slot + 1;
+      if (cons_slot == 0) cons_phase ^= 1;
     }
   }
 

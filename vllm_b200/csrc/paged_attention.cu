@@ -272,16 +272,16 @@ static int sm_count() {
   return cache[dev];
 }
 
-static DecodeKernelInfo find_decode(int d, int qdt, int kv, int gp) {
+static DecodeKernelInfo find_decode(int d, int qdt, int kv, int gp, int nt) {
   switch (d) {
-    case 32: return find_decode_d32(qdt, kv, gp);
-    case 64: return find_decode_d64(qdt, kv, gp);
-    case 80: return find_decode_d80(qdt, kv, gp);
-    case 96: return find_decode_d96(qdt, kv, gp);
-    case 112: return find_decode_d112(qdt, kv, gp);
-    case 128: return find_decode_d128(qdt, kv, gp);
-    case 192: return find_decode_d192(qdt, kv, gp);
-    case 256: return find_decode_d256(qdt, kv, gp);
+    case 32: return find_decode_d32(qdt, kv, gp, nt);
+    case 64: return find_decode_d64(qdt, kv, gp, nt);
+    case 80: return find_decode_d80(qdt, kv, gp, nt);
+    case 96: return find_decode_d96(qdt, kv, gp, nt);
+    case 112: return find_decode_d112(qdt, kv, gp, nt);
+    case 128: return find_decode_d128(qdt, kv, gp, nt);
+    case 192: return find_decode_d192(qdt, kv, gp, nt);
+    case 256: return find_decode_d256(qdt, kv, gp, nt);
   }
   return {nullptr, 0};
 }
@@ -435,13 +435,13 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
               aligned(a->out, 16) && (!split || aligned(a->tmp_out, 16)) &&
               (a->kv_block_stride * es) % 16 == 0 && (a->kv_head_stride * es) % 16 == 0 &&
               a->q_stride % 8 == 0;
-  if (fast) ki = find_decode(a->head_size, a->q_dtype, a->kv_dtype, gp);
+  if (fast) ki = find_decode(a->head_size, a->q_dtype, a->kv_dtype, gp, a->block_size / 16);
   DecodeLaunchFn fn = ki.fn;
   int rc;
   bool fused = false;
   if (fn != nullptr) {
     p.head_groups = (p.group + 8 * gp - 1) / (8 * gp);
-    const size_t stage_bytes = size_t(2) * a->head_size * a->block_size * es;
+    const size_t page_bytes = size_t(a->head_size) * a->block_size * es;
     // The partition prefix table lives in shared memory; very large batches run
     // without it (one work item per sequence and kv head).
     if (!split && a->max_seq_len > 64 && p.num_seqs <= 12000 &&
@@ -477,24 +477,30 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
       return B200PA_EUNSUPPORTED;
     }
     const size_t budget = budget_total - table_bytes - 1024 /* mbarriers */;
-    // Warps hide the latency of the per-page compute chain, stages the latency of HBM.
-    // Measured on B200: 16-bit caches run best with two stages per warp and as many
-    // warps as then fit (12 x 2 x 8 KiB for head size 128, block size 16); fp8 caches
-    // carry twice the instructions per byte and want the most warps first, even with a
-    // single stage.  B200PA_TUNE_WARPS / B200PA_TUNE_STAGES override the choice.
-    const size_t min_stages = es == 1 ? 1 : 2;
-    int nwarps = int(std::min<size_t>(size_t(ki.max_warps), budget / (min_stages * stage_bytes)));
-    if (nwarps > 4) nwarps &= ~3;  // same number of warps on each of the 4 schedulers
+    // Ring geometry.  Warps hide the latency of the per-page instruction chain, ring slots
+    // the latency of HBM; measured on B200 the first matters more and a shallow ring (about
+    // 100-130 KiB in flight per SM) beats a deep one.  Pages of 4 KiB and more get separate
+    // K and V slots; smaller pages share one slot and one barrier per block.
+    // B200PA_TUNE_SPLIT / _WARPS / _STAGES override (STAGES = slots per warp).
+    int split_kv = page_bytes >= 4096 ? 1 : 0;
+    if (const char* e = getenv("B200PA_TUNE_SPLIT")) split_kv = atoi(e) != 0;
+    const size_t slot_bytes = split_kv ? page_bytes : 2 * page_bytes;
+    const size_t min_slots = split_kv ? 2 : 1;
+    int nwarps = int(std::min<size_t>(size_t(ki.max_warps), budget / (min_slots * slot_bytes)));
+    if (es == 2 && nwarps > 12) nwarps = 12;  // 16-bit caches: 12 warps measured best
+    if (nwarps >= 8) nwarps &= ~3;  // same number of warps on each of the 4 schedulers
     if (nwarps < 1) nwarps = 1;
     if (const char* e = getenv("B200PA_TUNE_WARPS"))
       nwarps = std::max(1, std::min(ki.max_warps, atoi(e)));
-    int ns = int(std::min<size_t>(4, budget / (size_t(nwarps) * stage_bytes)));
-    if (const char* e = getenv("B200PA_TUNE_STAGES")) ns = std::max(1, std::min(ns, atoi(e)));
-    if (ns < 1) {
+    int ns = int(std::min<size_t>(split_kv ? 2 : 2, budget / (size_t(nwarps) * slot_bytes)));
+    if (const char* e = getenv("B200PA_TUNE_STAGES"))
+      ns = std::max(int(min_slots), std::min(int(budget / (size_t(nwarps) * slot_bytes)), atoi(e)));
+    if (ns < int(min_slots)) {
       set_error("head_size=%d block_size=%d does not fit the shared-memory pipeline", a->head_size,
                 a->block_size);
       return B200PA_EUNSUPPORTED;
     }
+    p.split_kv = split_kv;
     p.nstages = ns;
     unsigned* arrive = nullptr;
     p.status = device_status_ptr();
@@ -506,7 +512,7 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
     fused = split && int64_t(p.num_seqs) * p.num_kv_heads * p.head_groups <= kArrivePerRegion;
     p.arrive = fused ? arrive : nullptr;
     const size_t bars_bytes = (size_t(nwarps) * ns * 8 + 127) & ~size_t(127);
-    const size_t smem = table_bytes + bars_bytes + size_t(nwarps) * ns * stage_bytes;
+    const size_t smem = table_bytes + bars_bytes + size_t(nwarps) * ns * slot_bytes;
     const int grid = sm_count();
     cudaError_t e = fn(p, grid, nwarps * 32, smem, s);
     count_launch();
