@@ -186,14 +186,18 @@ struct Fp8Unpack {
 template <bool kE5M2, bool kAlu>
 __device__ __forceinline__ void fp8x4_to_f16(uint32_t x, uint32_t& lo, uint32_t& hi) {
   if constexpr (!kAlu) {
-    uint16_t l16, h16;
-    asm("mov.b32 {%0, %1}, %2;" : "=h"(l16), "=h"(h16) : "r"(x));
+    // one asm block, so that the assembler can read the two halves of `x` in place
+    // instead of materialising them in separate registers first
     if constexpr (kE5M2) {
-      asm("cvt.rn.f16x2.e5m2x2 %0, %1;" : "=r"(lo) : "h"(l16));
-      asm("cvt.rn.f16x2.e5m2x2 %0, %1;" : "=r"(hi) : "h"(h16));
+      asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\t"
+          "cvt.rn.f16x2.e5m2x2 %0, l;\n\tcvt.rn.f16x2.e5m2x2 %1, h;\n\t}"
+          : "=r"(lo), "=r"(hi)
+          : "r"(x));
     } else {
-      asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(lo) : "h"(l16));
-      asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(hi) : "h"(h16));
+      asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\t"
+          "cvt.rn.f16x2.e4m3x2 %0, l;\n\tcvt.rn.f16x2.e4m3x2 %1, h;\n\t}"
+          : "=r"(lo), "=r"(hi)
+          : "r"(x));
     }
   } else if constexpr (kE5M2) {
     lo = prmt(x, 0u, 0x1404u);
