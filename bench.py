@@ -123,6 +123,9 @@ def build_workload(name: str, device, world: int, rank: int, num_seqs=None):
             return W.config3(device, seed=rank, num_seqs=num_seqs), "v2", "weak"
         if name == "cfg5":
             return W.config5(device, world_size=world, rank=rank, num_seqs=num_seqs), "v2", "strong"
+    if name in ("cfg3w", "cfg3wf"):
+        # the KV-write step of config 3 (x-layout / flash layout): 128 new tokens per sequence
+        return W.config3(device, seed=rank, num_seqs=num_seqs or 128), name, "weak"
     if name == "cfg2":
         return W.config2(device, seed=0, rank=rank), "v2", "weak"
     if name == "cfg1":
@@ -196,7 +199,8 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"])
+    ap.add_argument("--workload", default="cfg2",
+                    choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "cfg3w", "cfg3wf"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--num-seqs", type=int, default=None,
                     help="override the batch size of cfg2/cfg3/cfg5 (small cases for profiler captures)")
@@ -253,12 +257,42 @@ def main() -> int:
     from vllm_b200 import capi
     from vllm_b200 import workloads as W
 
-    scratch = w.scratch()
-    out = torch.empty_like(w.query)
-    flush = None if w.attn_bytes() > 4 * 126e6 else torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    is_write = version in ("cfg3w", "cfg3wf")
+    if is_write:
+        # KV write: new K/V [T, Hkv, D] bf16 -> fp8 cache; flash layout uses [NB, B, H, D] caches
+        T = w.new_key.shape[0]
+        if version == "cfg3wf":
+            nb = w.key_cache.shape[0]
+            kcache = torch.zeros(nb, w.block_size, w.num_kv_heads, w.head_size, dtype=torch.uint8, device=dev)
+            vcache = torch.zeros_like(kcache)
+            write = ops.reshape_and_cache_flash
+        else:
+            kcache, vcache = w.key_cache, w.value_cache
+            write = ops.reshape_and_cache
+        units_rank = T
+        bytes_rank = w.reshape_bytes()
+        metric = "reshape_and_cache tokens/s"
+        kernel_name = "reshape_and_cache_flash_kernel" if version == "cfg3wf" else "reshape_and_cache_kernel"
+        cfg["workload"] = (f"{w.name} KV write ({'flash' if version == 'cfg3wf' else 'x'} layout): "
+                           f"{T} new tokens x {w.num_kv_heads} heads x {w.head_size}, bf16 -> fp8-e4m3, "
+                           f"block_size={w.block_size}")
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        cfg["l2"] = "256 MB scratch written between timed calls"
+        nk, nv, sm = w.new_key, w.new_value, w.slot_mapping
 
-    def step():
-        W.run_attention(w, out=out, version=version, scratch=scratch)
+        def step():
+            write(nk, nv, kcache, vcache, sm, "fp8", w.k_scale, w.v_scale)
+    else:
+        scratch = w.scratch()
+        out = torch.empty_like(w.query)
+        flush = None if w.attn_bytes() > 4 * 126e6 else torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        units_rank = w.num_seqs
+        bytes_rank = w.attn_bytes()
+        metric = METRIC
+        kernel_name = "pa_decode_kernel (split-KV merge fused; one launch per step)"
+
+        def step():
+            W.run_attention(w, out=out, version=version, scratch=scratch)
 
     def barrier():
         if dist:
@@ -290,41 +324,59 @@ def main() -> int:
     ms = float(np.mean(per_step))
     clocks = sampler.stop()
 
-    # ---- end to end with host step inputs
-    hq = w.query.cpu().pin_memory()
-    hbt = w.block_tables.cpu().pin_memory()
-    hsl = w.seq_lens.cpu().pin_memory()
-    hout = torch.empty_like(hq).pin_memory()
-    dq, dbt, dsl = torch.empty_like(w.query), torch.empty_like(w.block_tables), torch.empty_like(w.seq_lens)
-    wq, wbt, wsl = w.query, w.block_tables, w.seq_lens
+    # ---- end to end with host step inputs (pinned), one event pair per step so that the
+    # L2 flush of small workloads stays outside the timed intervals
+    if is_write:
+        hk, hv, hs = nk.cpu().pin_memory(), nv.cpu().pin_memory(), sm.cpu().pin_memory()
+        dk, dv, ds = torch.empty_like(nk), torch.empty_like(nv), torch.empty_like(sm)
+        done = torch.zeros(1, dtype=torch.int32, device=dev)
+        hdone = torch.zeros(1, dtype=torch.int32).pin_memory()
 
-    def e2e_step():
-        dq.copy_(hq, non_blocking=True)
-        dbt.copy_(hbt, non_blocking=True)
-        dsl.copy_(hsl, non_blocking=True)
-        w.query, w.block_tables, w.seq_lens = dq, dbt, dsl
-        W.run_attention(w, out=out, version=version, scratch=scratch)
-        hout.copy_(out, non_blocking=True)
+        def e2e_step():
+            dk.copy_(hk, non_blocking=True)
+            dv.copy_(hv, non_blocking=True)
+            ds.copy_(hs, non_blocking=True)
+            write(dk, dv, kcache, vcache, ds, "fp8", w.k_scale, w.v_scale)
+            hdone.copy_(done, non_blocking=True)  # the step's result is the updated cache; read a token back
+
+        h2d = hk.numel() * 2 + hv.numel() * 2 + hs.numel() * 8
+        d2h = 4
+    else:
+        hq = w.query.cpu().pin_memory()
+        hbt = w.block_tables.cpu().pin_memory()
+        hsl = w.seq_lens.cpu().pin_memory()
+        hout = torch.empty_like(hq).pin_memory()
+        dq, dbt, dsl = torch.empty_like(w.query), torch.empty_like(w.block_tables), torch.empty_like(w.seq_lens)
+        wq, wbt, wsl = w.query, w.block_tables, w.seq_lens
+
+        def e2e_step():
+            dq.copy_(hq, non_blocking=True)
+            dbt.copy_(hbt, non_blocking=True)
+            dsl.copy_(hsl, non_blocking=True)
+            w.query, w.block_tables, w.seq_lens = dq, dbt, dsl
+            W.run_attention(w, out=out, version=version, scratch=scratch)
+            hout.copy_(out, non_blocking=True)
+
+        h2d = hq.numel() * hq.element_size() + hbt.numel() * 4 + hsl.numel() * 4
+        d2h = hout.numel() * hout.element_size()
 
     for _ in range(3):
         e2e_step()
     barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(a.steps):
+    evs2 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(a.steps)]
+    for s_ev, e_ev in evs2:
         if flush is not None:
             flush.zero_()
+        s_ev.record()
         e2e_step()
-    e1.record()
+        e_ev.record()
     barrier()
-    ms_e2e = e0.elapsed_time(e1) / a.steps
-    w.query, w.block_tables, w.seq_lens = wq, wbt, wsl
-    h2d = hq.numel() * hq.element_size() + hbt.numel() * 4 + hsl.numel() * 4
-    d2h = hout.numel() * hout.element_size()
+    ms_e2e = float(np.mean([s_ev.elapsed_time(e_ev) for s_ev, e_ev in evs2]))
+    if not is_write:
+        w.query, w.block_tables, w.seq_lens = wq, wbt, wsl
 
     # ---- max over ranks, whole-job aggregate
-    seqs_total = w.num_seqs
-    bytes_rank = w.attn_bytes()
+    seqs_total = units_rank
     if dist:
         t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
         td.all_reduce(t, op=td.ReduceOp.MAX)
@@ -338,7 +390,7 @@ def main() -> int:
         achieved = bytes_rank / (ms * 1e-3) / 1e9
         ratio = NCU_TRAFFIC_RATIO.get(a.workload)
         line = {
-            "metric": METRIC, "value": seqs_total / (ms * 1e-3), "unit": "tokens/s",
+            "metric": metric, "value": seqs_total / (ms * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic", "config": cfg, "clocks": clocks,
@@ -352,12 +404,12 @@ def main() -> int:
                 "frac_of_nominal_8TBs": achieved / 8000.0,
                 "traffic": None if ratio is None else ratio * bytes_rank,
                 "algorithmic_bytes_per_launch": int(bytes_rank),
-                "kernel": "pa_decode_kernel (split-KV merge fused; one launch per step)",
+                "kernel": kernel_name,
                 "ms_min": float(np.min(per_step)), "ms_median": float(np.median(per_step)),
             },
             "wall_s_timed_region": t_wall,
         }
-        if world == 1 and not a.no_cpu_baseline:
+        if world == 1 and not a.no_cpu_baseline and not is_write:
             try:
                 leg = cpu_reference_leg(w, steps=5, warmup=1)
             except Exception as ex:  # the baseline must never take the GPU number down with it

@@ -142,3 +142,37 @@ def test_write_then_attend_uses_the_written_tokens():
     k0, _ = O.gather_kv(kc, vc, w.block_tables.cpu()[0], 1024, "fp8", 1.0, 1.0, torch.float32)
     qk = O.quantize_fp8(w.new_key[:128].cpu(), float(w.k_scale), "fp8").view(torch.float8_e4m3fn).float()
     assert torch.equal(k0[-128:], qk)
+
+
+def test_fp8_quantiser_fp32_inputs_ties_and_odd_scales():
+    """The quantiser must give the bits of cvt(x / scale) with an IEEE division for arbitrary
+    fp32 inputs: random bit patterns (specials included), inputs built to sit on and next to
+    fp8 rounding ties, and awkward scales (a reciprocal multiply would fail here)."""
+    g = torch.Generator().manual_seed(3)
+    n = 1 << 21
+    rand_bits = torch.randint(-(1 << 31), (1 << 31) - 1, (n,), generator=g, dtype=torch.int64).to(torch.int32)
+    x_rand = rand_bits.view(torch.float32)
+    x_norm = torch.randn(n, generator=g) * 3
+    scales = [1.0, 0.011826, 3.7, 1 / 3, 5.3 / 448, 2.0 ** -20, 1.0000001, 0.9999999, 123456.7,
+              float(torch.rand(1, generator=g)) + 1e-3]
+    for kv in ("fp8", "fp8_e5m2"):
+        dt, fmax = O.FP8_FORMATS[kv]
+        # every finite fp8 value and the midpoints between neighbours, times the scale, +- a few ulps
+        codes = torch.arange(256, dtype=torch.int16).to(torch.uint8).view(dt).float()
+        vals = torch.sort(codes[torch.isfinite(codes)]).values
+        mids = (vals[1:] + vals[:-1]) / 2
+        for scale in scales:
+            s32 = torch.tensor(scale, dtype=torch.float32)
+            base = torch.cat([mids, vals]) * s32
+            near = torch.cat([torch.nextafter(base, torch.tensor(float("inf"))),
+                              torch.nextafter(base, torch.tensor(-float("inf"))), base])
+            for _ in range(2):
+                near = torch.cat([near, torch.nextafter(near, torch.tensor(float("inf"))),
+                                  torch.nextafter(near, torch.tensor(-float("inf")))])
+            x = torch.cat([near, x_norm * s32 * 100, x_rand])
+            dst = torch.empty(x.numel(), dtype=torch.uint8, device=DEV)
+            ops.convert_fp8(dst, x.to(DEV), float(s32), kv)
+            want = O.quantize_fp8(x, float(s32), kv)
+            bad = torch.nonzero(dst.cpu() != want).flatten()
+            assert bad.numel() == 0, (kv, scale, bad.numel(), x[bad[:4]].tolist(),
+                                      dst.cpu()[bad[:4]].tolist(), want[bad[:4]].tolist())
