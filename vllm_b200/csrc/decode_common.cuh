@@ -78,13 +78,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait: false if the phase did not complete within ~2^32 SM cycles
-// (about two seconds) or 2^24 polls, whichever comes first.
+// Bounded wait: false if the phase did not complete within ~2^32 SM cycles (about two
+// seconds).  The clock is read only every 64 polls to keep waiting warps cheap.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  for (int i = 0; i < (1 << 24); ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+  for (int outer = 0; outer < (1 << 20); ++outer) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
     if (clock64() - t0 > (1ll << 32)) break;
   }
   return false;
