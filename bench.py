@@ -45,7 +45,7 @@ FALLBACK_HBM_GBS = 6650.0
 # algorithmic bytes of that launch, from the ncu capture summarised in
 # profiles/pa_decode_kernel_cfg2.md and profiles/pa_decode_kernel_cfg3_fp8.md (small cases of the
 # same kernels; traffic grows in proportion to tokens).
-NCU_TRAFFIC_RATIO = {"cfg2": 1.015, "cfg4": 1.015, "cfg3": 1.020, "cfg5": 1.020}
+NCU_TRAFFIC_RATIO = {"cfg2": 1.019, "cfg4": 1.019, "cfg3": 1.027, "cfg5": 1.027}
 
 
 def measured_peak():
