@@ -42,9 +42,9 @@ sys.path.insert(0, str(ROOT))
 METRIC = "paged_attention decode tokens/s"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode-kernel launch divided by the
-# algorithmic bytes of that launch, from the ncu capture summarised in
-# profiles/pa_decode_kernel_cfg2.md and profiles/pa_decode_kernel_cfg3_fp8.md (small cases of the
-# same kernels; traffic grows in proportion to tokens).
+# algorithmic bytes of that launch, from ncu captures of small cases of the same kernels (64
+# sequences of the bf16 workload, 16 sequences of the fp8 workload; their summaries are kept with
+# the other profiler summaries of this repository).  Traffic grows in proportion to tokens.
 NCU_TRAFFIC_RATIO = {"cfg2": 1.019, "cfg4": 1.019, "cfg3": 1.027, "cfg5": 1.027}
 
 

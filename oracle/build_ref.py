@@ -125,7 +125,9 @@ def build_cpu(ref: Path, force: bool) -> None:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("VLLM_REFERENCE_DIR", "/root/reference"))
+    # default: $VLLM_REFERENCE_DIR, else a checkout named "reference" beside this repository
+    ap.add_argument("--reference", default=os.environ.get("VLLM_REFERENCE_DIR",
+                                                          str(HERE.parent.parent / "reference")))
     ap.add_argument("--only", choices=["cuda", "cpu"])
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()
