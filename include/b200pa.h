@@ -127,13 +127,19 @@ typedef struct b200pa_attn_args {
   int32_t blocksparse_head_sliding_step;
 } b200pa_attn_args;
 
-/* Replaces paged_attention_v1 (csrc/attention/paged_attention_v1.cu:160-182):
- * whole sequence per work item, no scratch. */
+/* Replaces paged_attention_v1 (csrc/attention/paged_attention_v1.cu:160-182).  No scratch
+ * argument, as in the reference; long sequences of small batches are nevertheless split
+ * across work items through a 32 MiB workspace inside the library (partials of at most
+ * that size, else one work item per sequence and kv head).  That workspace is shared by
+ * all calls on a device: calls that overlap on the GPU (different streams without an
+ * ordering between them) must not both be small-batch attention calls. */
 int b200pa_paged_attention_v1(const b200pa_attn_args* args, void* stream);
 
 /* Replaces paged_attention_v2 + its reduce kernel
  * (csrc/attention/paged_attention_v2.cu:167-192, attention_kernels.cuh:559-664):
- * split-KV over 512-token partitions using the caller's scratch. */
+ * split-KV over 512-token partitions using the caller's scratch, merged inside the same
+ * kernel.  Batches too small to fill the GPU with 512-token partitions are split finer
+ * through the library workspace described at b200pa_paged_attention_v1 instead. */
 int b200pa_paged_attention_v2(const b200pa_attn_args* args, void* stream);
 
 /*

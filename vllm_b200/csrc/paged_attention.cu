@@ -208,11 +208,12 @@ constexpr int kArriveRegions = 8;
 constexpr int kArrivePerRegion = 16384;
 __device__ unsigned g_arrive[kArriveRegions][kArrivePerRegion];
 
-// Split-KV workspace of paged_attention_v1.  The reference's v1 has no scratch
-// argument, so a sequence could only be handled by one work item; with a small batch
-// that leaves most of the GPU idle.  v1 therefore splits sequences into partitions of
-// 64..512 tokens when the partials fit this buffer, exactly like v2 does with the
-// caller's scratch.  Shared by all v1 calls on a device (one stream at a time).
+// Split-KV workspace of the library.  The reference's v1 has no scratch argument, so a
+// sequence could only be handled by one work item; with a small batch that leaves most of
+// the GPU idle.  v1 therefore splits sequences into partitions of 64..512 tokens when the
+// partials fit this buffer, exactly like v2 does with the caller's scratch; v2 switches to
+// it as well when the caller's 512-token partitions are too coarse to fill the GPU.
+// Shared by all such calls on a device (one stream at a time).
 constexpr size_t kV1ScratchBytes = size_t(32) << 20;
 static __device__ __align__(256) unsigned char g_v1_scratch[kV1ScratchBytes];
 
@@ -444,29 +445,31 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
     const size_t page_bytes = size_t(a->head_size) * a->block_size * es;
     // The partition prefix table lives in shared memory; very large batches run
     // without it (one work item per sequence and kv head).
-    if (!split && a->max_seq_len > 64 && p.num_seqs <= 12000 &&
-        !getenv("B200PA_TUNE_NO_V1_SPLIT")) {
-      // No caller scratch (v1, or v2 with a single 512-token partition): split into the
-      // library's own workspace.  Partition size: 512 tokens, refined down to 64 while the
+    if (a->max_seq_len > 64 && p.num_seqs <= 12000 && !getenv("B200PA_TUNE_NO_V1_SPLIT")) {
+      // Split-KV into the library's own workspace when the caller gave no scratch (v1, or v2
+      // with a single 512-token partition) or when the caller's 512-token partitions are too
+      // coarse to fill the GPU.  Partition size: 512 tokens, refined down to 64 while the
       // batch still has fewer than ~4 work items per resident warp.
       const int64_t warps_total = int64_t(sm_count()) * 12;
       const int64_t units = int64_t(p.num_seqs) * p.num_kv_heads * p.head_groups;
       int pt = kPartitionTokens;
       while (pt > 64 && units * ((a->max_seq_len + pt / 2 - 1) / (pt / 2)) <= 4 * warps_total) pt /= 2;
-      const int64_t parts = (int64_t(a->max_seq_len) + pt - 1) / pt;
-      const int64_t n = int64_t(p.num_seqs) * p.num_heads * parts;
-      auto up = [](int64_t v) { return (v + 255) & ~int64_t(255); };
-      const int64_t stat = up(n * 4);
-      const int64_t need = 2 * stat + up(n * a->head_size * 2);
-      unsigned char* ws = (parts > 1 && need <= int64_t(kV1ScratchBytes) &&
-                           units <= kArrivePerRegion) ? v1_scratch_ptr() : nullptr;
-      if (ws != nullptr) {
-        split = true;
-        p.part_tokens = pt;
-        p.max_partitions = int(parts);
-        p.exp_sums = reinterpret_cast<float*>(ws);
-        p.max_logits = reinterpret_cast<float*>(ws + stat);
-        p.tmp_out = ws + 2 * stat;
+      if (!split || pt < kPartitionTokens) {
+        const int64_t parts = (int64_t(a->max_seq_len) + pt - 1) / pt;
+        const int64_t n = int64_t(p.num_seqs) * p.num_heads * parts;
+        auto up = [](int64_t v) { return (v + 255) & ~int64_t(255); };
+        const int64_t stat = up(n * 4);
+        const int64_t need = 2 * stat + up(n * a->head_size * 2);
+        unsigned char* ws = (parts > 1 && need <= int64_t(kV1ScratchBytes) &&
+                             units <= kArrivePerRegion) ? v1_scratch_ptr() : nullptr;
+        if (ws != nullptr) {
+          split = true;
+          p.part_tokens = pt;
+          p.max_partitions = int(parts);
+          p.exp_sums = reinterpret_cast<float*>(ws);
+          p.max_logits = reinterpret_cast<float*>(ws + stat);
+          p.tmp_out = ws + 2 * stat;
+        }
       }
     }
     p.use_table = split ? 1 : 0;
