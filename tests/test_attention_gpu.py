@@ -287,3 +287,26 @@ def test_block_sparse_pattern(version, step, ref_cuda_ops):
             e, m, t = w.scratch()
             ref_cuda_ops[0].paged_attention_v2(r, e, m, t, *tail)
         torch.testing.assert_close(out.float(), r.float(), atol=1e-2, rtol=1e-2)
+
+
+def test_lengths_beyond_max_seq_len_do_not_overrun_the_scratch():
+    """A caller bug the reference tolerates silently (its v2 grid simply has no partition for
+    the excess tokens): seq_lens larger than max_seq_len must not write past the scratch."""
+    w = W.small(DEV, seed=13, num_seqs=4, num_heads=8, num_kv_heads=2, max_len=2000, num_blocks=700)
+    S, Hq, D = w.query.shape
+    P = 2  # scratch sized for max_seq_len = 1024 although sequences reach 2000 tokens
+    canary = 7.0
+    exp_sums = torch.full((S, Hq, P + 1), canary, device=DEV)
+    max_logits = torch.full((S, Hq, P + 1), canary, device=DEV)
+    tmp_out = torch.full((S, Hq, P + 1, D), canary, device=DEV, dtype=w.query.dtype)
+    out = torch.empty_like(w.query)
+    ops.paged_attention_v2(out, exp_sums[:, :, :P].contiguous(), max_logits[:, :, :P].contiguous(),
+                           tmp_out[:, :, :P].contiguous(), w.query, w.key_cache, w.value_cache,
+                           w.num_kv_heads, w.scale, w.block_tables, w.seq_lens, w.block_size, 1024,
+                           None, "auto", w.k_scale, w.v_scale)
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    # equals attention over the first 1024 tokens of every sequence
+    w.seq_lens = torch.clamp(w.seq_lens, max=1024)
+    want = W.run_attention(w, version="v2")
+    torch.testing.assert_close(out.float(), want.float(), atol=1e-2, rtol=1e-2)

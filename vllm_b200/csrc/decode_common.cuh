@@ -36,7 +36,8 @@ struct DecodeParams {
   int block_size;
   int max_blocks_per_seq;
   int max_partitions;  // P; 0 = unsplit: one work item covers the whole sequence
-  int part_tokens;     // tokens per partition (512 for v2; v1 may split finer into library scratch)
+  int part_tokens;     // tokens per partition (512 with caller scratch; 64..512 in the library workspace)
+  int len_cap;         // sequence lengths are clamped to this (max_partitions * part_tokens when split)
   int group;           // query heads per kv head
   int head_groups;     // ceil(group / heads per item)
   int nstages;         // ring slots per warp
@@ -164,52 +165,22 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-  uint32_t d;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
-  return d;
-}
-
-// Four fp8 bytes -> two packed f16x2 (lo = bytes 0,1; hi = bytes 2,3).
-//
-// kAlu = false: cvt.rn.f16x2.e4m3x2 (exact values).  That instruction issues on the
-//   narrow XU pipe, which saturates near HBM rate when every K and V byte goes through it.
-// kAlu = true: integer ALU ops only.  e4m3 codes are placed into the f16 bit pattern
-//   without re-biasing the exponent, so they come out as value * 2^-8 (exact,
-//   subnormals included) and the caller folds 2^8 into its scale; e4m3 NaN codes
-//   (0x7F / 0xFF) decode as +-480 * 2^-8 rather than NaN.  e5m2 is the upper byte of
-//   an f16, so it comes out unscaled.
-// The decode kernel sends K through one pipe and V through the other.
-template <bool kE5M2, bool kAlu>
-struct Fp8Unpack {
-  static constexpr float kPrescale = (kAlu && !kE5M2) ? 256.f : 1.f;
-};
-
-template <bool kE5M2, bool kAlu>
+// Four fp8 bytes -> two packed f16x2 (lo = bytes 0,1; hi = bytes 2,3), exact.
+// One asm block, so that the assembler can read the two halves of `x` in place.
+// (Unpacking with integer ALU ops instead, or feeding the bytes to the legacy fp8
+// mma.sync, were both measured slower on B200.)
+template <bool kE5M2>
 __device__ __forceinline__ void fp8x4_to_f16(uint32_t x, uint32_t& lo, uint32_t& hi) {
-  if constexpr (!kAlu) {
-    // one asm block, so that the assembler can read the two halves of `x` in place
-    // instead of materialising them in separate registers first
-    if constexpr (kE5M2) {
-      asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\t"
-          "cvt.rn.f16x2.e5m2x2 %0, l;\n\tcvt.rn.f16x2.e5m2x2 %1, h;\n\t}"
-          : "=r"(lo), "=r"(hi)
-          : "r"(x));
-    } else {
-      asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\t"
-          "cvt.rn.f16x2.e4m3x2 %0, l;\n\tcvt.rn.f16x2.e4m3x2 %1, h;\n\t}"
-          : "=r"(lo), "=r"(hi)
-          : "r"(x));
-    }
-  } else if constexpr (kE5M2) {
-    lo = prmt(x, 0u, 0x1404u);
-    hi = prmt(x, 0u, 0x3424u);
+  if constexpr (kE5M2) {
+    asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\t"
+        "cvt.rn.f16x2.e5m2x2 %0, l;\n\tcvt.rn.f16x2.e5m2x2 %1, h;\n\t}"
+        : "=r"(lo), "=r"(hi)
+        : "r"(x));
   } else {
-    const uint32_t t = (x >> 1) & 0x3F3F3F3Fu;          // exponent + top mantissa bits
-    const uint32_t hb = (x & 0x80808080u) | t;           // high byte of each f16: s0eeeemm
-    const uint32_t lb = (x << 7) & 0x80808080u;          // low byte of each f16: m0000000
-    lo = prmt(lb, hb, 0x5140u);
-    hi = prmt(lb, hb, 0x7362u);
+    asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\t"
+        "cvt.rn.f16x2.e4m3x2 %0, l;\n\tcvt.rn.f16x2.e4m3x2 %1, h;\n\t}"
+        : "=r"(lo), "=r"(hi)
+        : "r"(x));
   }
 }
 

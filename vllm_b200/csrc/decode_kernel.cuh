@@ -21,7 +21,7 @@
 //     operands these products need, so pages are used as they land, untransposed.
 //     P^T is produced from the S^T accumulators with one movmatrix per 8 tokens.
 //   * fp8 caches are dequantised after ldmatrix (4 bytes per lane) with
-//     integer ALU ops (see fp8x4_to_f16); the dot-product index order inside a 16-wide k-step is
+//     cvt.rn.f16x2.e4m3x2; the dot-product index order inside a 16-wide k-step is
 //     permuted consistently in Q / P, which is free.  k_scale is folded into the
 //     logit scale and v_scale into the output scale.
 //   * Online softmax in the log2 domain, fp32 state, warp-shuffle reductions.
@@ -68,7 +68,7 @@ __device__ __forceinline__ int load_bt(const DecodeParams& p, const WorkItem& it
   return __ldg(p.block_tables + int64_t(it.seq) * p.max_blocks_per_seq + it.first_page + pg);
 }
 
-template <typename QT, int KV, int D, int GP, int NT, int MAXW, int CVT = 2>
+template <typename QT, int KV, int D, int GP, int NT, int MAXW>
 __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodeParams p) {
   using TR = DecodeTraits<QT, KV, D, GP>;
   constexpr bool kFp8 = TR::kFp8;
@@ -77,11 +77,6 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
   constexpr int KS = TR::kKSteps;
   constexpr bool kE5 = KV == kCacheE5M2;
   constexpr bool kOutBf = std::is_same_v<QT, __nv_bfloat16>;
-  // fp8 unpacking pipe per operand: CVT 0 = K and V on the ALU, 1 = K on the XU and V
-  // on the ALU (balanced), 2 = both on the XU
-  constexpr bool kAluK = CVT == 0;
-  constexpr bool kAluV = CVT != 2;
-
   extern __shared__ __align__(128) unsigned char smem_raw[];
 
   const int lane = threadIdx.x & 31;
@@ -118,7 +113,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
     const int s1 = min(S, s0 + per);
     int mine = 0;
     for (int s = s0; s < s1; ++s) {
-      const int len = p.seq_lens[s];
+      const int len = min(p.seq_lens[s], p.len_cap);
       mine += max(1, (len + PT - 1) / PT);
     }
     int incl = mine;
@@ -134,7 +129,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
     int run = base + incl - mine;
     for (int s = s0; s < s1; ++s) {
       cum[s] = run;
-      const int len = p.seq_lens[s];
+      const int len = min(p.seq_lens[s], p.len_cap);
       run += max(1, (len + PT - 1) / PT);
     }
     if (threadIdx.x == blockDim.x - 1) cum[S] = run;
@@ -180,7 +175,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
       it.part = cg - cum[lo];
       it.nparts = cum[lo + 1] - cum[lo];
       it.tok_begin = it.part * PT;
-      it.tok_end = min(p.seq_lens[lo], it.tok_begin + PT);
+      it.tok_end = min(min(p.seq_lens[lo], p.len_cap), it.tok_begin + PT);
     } else {
       it.seq = cg;
       it.tok_begin = 0;
@@ -248,10 +243,9 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
 
   while (inflight < NSLOT && produce_one()) {}
 
-  // fp8 values come out of fp8x4_to_f16 scaled by 1/kPrescale; fold that and the
-  // per-tensor scales into the logit scale and the output scale
-  const float kv_qk = kFp8 ? *p.k_scale * Fp8Unpack<kE5, kAluK>::kPrescale : 1.f;
-  const float kv_o = kFp8 ? *p.v_scale * Fp8Unpack<kE5, kAluV>::kPrescale : 1.f;
+  // fold the per-tensor scales of an fp8 cache into the logit scale and the output scale
+  const float kv_qk = kFp8 ? *p.k_scale : 1.f;
+  const float kv_o = kFp8 ? *p.v_scale : 1.f;
   const float qk_scale = p.scale * kLog2e * kv_qk;
   bool failed = false;
 
@@ -354,10 +348,10 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
             for (int ks = 0; ks + 1 < KS; ks += 2) {
               uint32_t r0, r1, r2, r3, a0, a1, a2, a3, b0, b1, b2, b3;
               ldsm_x4(kaddr + uint32_t(ks * B * 16), r0, r1, r2, r3);
-              fp8x4_to_f16<kE5, kAluK>(r0, a0, a2);
-              fp8x4_to_f16<kE5, kAluK>(r1, a1, a3);
-              fp8x4_to_f16<kE5, kAluK>(r2, b0, b2);
-              fp8x4_to_f16<kE5, kAluK>(r3, b1, b3);
+              fp8x4_to_f16<kE5>(r0, a0, a2);
+              fp8x4_to_f16<kE5>(r1, a1, a3);
+              fp8x4_to_f16<kE5>(r2, b0, b2);
+              fp8x4_to_f16<kE5>(r3, b1, b3);
 #pragma unroll
               for (int nt = 0; nt < GP; ++nt) {
                 mma16816<false>(s[t][nt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
@@ -369,8 +363,8 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
               uint32_t r0, r1, a0, a1, a2, a3;
               // lanes 0-15 supply the addresses of the two matrices (lanes 16-31 ignored)
               ldsm_x2(sk + uint32_t((ks * B + tt + tok) * 16), r0, r1);
-              fp8x4_to_f16<kE5, kAluK>(r0, a0, a2);
-              fp8x4_to_f16<kE5, kAluK>(r1, a1, a3);
+              fp8x4_to_f16<kE5>(r0, a0, a2);
+              fp8x4_to_f16<kE5>(r1, a1, a3);
 #pragma unroll
               for (int nt = 0; nt < GP; ++nt)
                 mma16816<false>(s[t][nt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
@@ -514,10 +508,10 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
             for (int mt = 0; mt + 1 < KS; mt += 2) {
               uint32_t r0, r1, r2, r3, a0, a1, a2, a3, b0, b1, b2, b3;
               ldsm_x4(vaddr + uint32_t(16 * mt * B), r0, r1, r2, r3);
-              fp8x4_to_f16<kE5, kAluV>(r0, a0, a2);
-              fp8x4_to_f16<kE5, kAluV>(r1, a1, a3);
-              fp8x4_to_f16<kE5, kAluV>(r2, b0, b2);
-              fp8x4_to_f16<kE5, kAluV>(r3, b1, b3);
+              fp8x4_to_f16<kE5>(r0, a0, a2);
+              fp8x4_to_f16<kE5>(r1, a1, a3);
+              fp8x4_to_f16<kE5>(r2, b0, b2);
+              fp8x4_to_f16<kE5>(r3, b1, b3);
 #pragma unroll
               for (int nt = 0; nt < GP; ++nt) {
                 mma16816<false>(o[mt][nt], a0, a1, a2, a3, pf[nt][0], pf[nt][1]);
@@ -528,8 +522,8 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
               constexpr int mt = KS - 1;
               uint32_t r0, r1, a0, a1, a2, a3;
               ldsm_x2(sv + uint32_t((16 * mt + ((lane >> 3) & 1) * 8 + (lane & 7)) * B + tt), r0, r1);
-              fp8x4_to_f16<kE5, kAluV>(r0, a0, a2);
-              fp8x4_to_f16<kE5, kAluV>(r1, a1, a3);
+              fp8x4_to_f16<kE5>(r0, a0, a2);
+              fp8x4_to_f16<kE5>(r1, a1, a3);
 #pragma unroll
               for (int nt = 0; nt < GP; ++nt)
                 mma16816<false>(o[mt][nt], a0, a1, a2, a3, pf[nt][0], pf[nt][1]);

@@ -7,6 +7,7 @@
 #include <algorithm>
 #include <atomic>
 #include <cfloat>
+#include <cstdint>
 #include <cstdlib>
 #include <iterator>
 
@@ -31,7 +32,7 @@ __global__ void pa_reduce_kernel(QT* __restrict__ out, const QT* __restrict__ tm
   if (item >= num_seqs * num_heads) return;
   const int seq = item / num_heads;
   const int len = seq_lens[seq];
-  const int np = (len + part_tokens - 1) / part_tokens;
+  const int np = min((len + part_tokens - 1) / part_tokens, max_partitions);
   if (np <= 1) return;
   float* w = s_w + warp * max_partitions;
   const float* ml = max_logits + int64_t(item) * max_partitions;
@@ -87,8 +88,8 @@ pa_generic_kernel(const DecodeParams p, int head_size, int x) {
   const int part = int(item % P);
   const int head = int((item / P) % p.num_heads);
   const int seq = int(item / (int64_t(P) * p.num_heads));
-  const int len = p.seq_lens[seq];
   const bool split = p.max_partitions > 0;
+  const int len = split ? min(p.seq_lens[seq], p.max_partitions * p.part_tokens) : p.seq_lens[seq];
   const int PT = p.part_tokens;
   const int nparts = split ? max(1, (len + PT - 1) / PT) : 1;
   if (part >= nparts) return;
@@ -472,6 +473,10 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
         }
       }
     }
+    // lengths beyond what the scratch has partitions for are ignored, like the reference's v2
+    // grid ignores partitions beyond max_num_partitions
+    p.len_cap = split ? int(std::min<int64_t>(int64_t(p.max_partitions) * p.part_tokens, INT32_MAX))
+                      : INT32_MAX;
     p.use_table = split ? 1 : 0;
     size_t table_bytes = p.use_table ? size_t((p.num_seqs + 1 + 3) & ~3) * 4 : 0;
     const size_t budget_total = 227 * 1024 - 1024;  // static smem + slack
