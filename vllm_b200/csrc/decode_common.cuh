@@ -41,7 +41,6 @@ struct DecodeParams {
   int group;           // query heads per kv head
   int head_groups;     // ceil(group / heads per item)
   int nstages;         // ring slots per warp
-  int split_kv;        // 1: K and V pages in separate slots; 0: one slot per block (K + V)
   int use_table;       // 1: per-sequence partition prefix table in shared memory
   float scale;
   // block-sparse attention of the reference signature (generic kernel only); enabled when

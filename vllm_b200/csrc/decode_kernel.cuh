@@ -87,11 +87,11 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
   constexpr int B = 16 * NT;  // tokens per cache block (16 or 32)
   constexpr uint32_t page_bytes = uint32_t(D) * B * (KV != kCache16 ? 1 : 2);
   const int NSLOT = p.nstages;  // ring slots of this warp
-  // split_kv: a slot holds one K page or one V page, each with its own barrier (finer
-  // prefetch granularity, pays off for pages >= 4 KiB); else a slot holds the K and the V
-  // page of one block behind one barrier (half the barrier traffic, better for small pages)
-  const bool split_kv = p.split_kv != 0;
-  const uint32_t slot_bytes = split_kv ? page_bytes : 2 * page_bytes;
+  // Pages of 4 KiB and more get one slot and one barrier each for K and V (finer prefetch
+  // granularity: the K slot is refilled while the softmax runs); smaller pages share one slot
+  // and one barrier per block (half the barrier traffic).  The host uses the same rule.
+  constexpr bool split_kv = page_bytes >= 4096;
+  constexpr uint32_t slot_bytes = split_kv ? page_bytes : 2 * page_bytes;
   const int PT = p.part_tokens;  // tokens per split-KV partition (a multiple of the block size)
 
   // ---- shared memory carve-up: [partition prefix table][mbarriers][stages]
@@ -201,29 +201,41 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
   int inflight = 0;
   int cons_slot = 0;
   uint32_t cons_phase = 0;
+  // the producer's own copy of the item it is loading (no cur/nxt selects in the hot path)
+  int pi_npages = cur.npages, pi_bt = cur.bt, pi_win = 0;
+  int64_t pi_kvoff = int64_t(cur.kvh) * p.kv_head_stride * ES;
+  const int64_t blk_stride_bytes = p.kv_block_stride * ES;
+
+  auto producer_take = [&](const WorkItem& it) {
+    pi_npages = it.npages;
+    pi_bt = it.bt;
+    pi_win = 0;
+    pi_kvoff = int64_t(it.kvh) * p.kv_head_stride * ES;
+    prod_pg = 0;
+  };
 
   auto produce_one = [&]() -> bool {
-    if (prod_half == 0) {
-      if (prod_sel == 0 && prod_pg >= cur.npages) {
+    if (!split_kv || prod_half == 0) {
+      if (prod_pg >= pi_npages) {
+        // the item is fully requested: move on to the next one, if it is known
+        if (prod_sel == 1 || !nxt.valid) return false;
         prod_sel = 1;
-        prod_pg = 0;
+        producer_take(nxt);
+        if (pi_npages == 0) return false;
       }
-      if (prod_sel == 1 && (!nxt.valid || prod_pg >= nxt.npages)) return false;
-      WorkItem& it = prod_sel ? nxt : cur;
       const int win = prod_pg >> 5;
-      if (win != it.win) {
-        it.win = win;
-        it.bt = load_bt(p, it, win, lane);
+      if (win != pi_win) {
+        pi_win = win;
+        pi_bt = load_bt(p, prod_sel ? nxt : cur, win, lane);
       }
-      prod_blk = __shfl_sync(0xffffffffu, it.bt, prod_pg & 31);
+      prod_blk = __shfl_sync(0xffffffffu, pi_bt, prod_pg & 31);
     }
     if (lane == 0) {
-      const int kvh = prod_sel ? nxt.kvh : cur.kvh;
-      const int64_t off = (int64_t(prod_blk) * p.kv_block_stride + int64_t(kvh) * p.kv_head_stride) * ES;
+      const int64_t off = int64_t(prod_blk) * blk_stride_bytes + pi_kvoff;
       const uint32_t bar = my_bar0 + prod_slot * 8;
       const uint32_t dst = my_slot0 + prod_slot * slot_bytes;
       mbar_expect_tx(bar, slot_bytes);
-      if (split_kv) {
+      if constexpr (split_kv) {
         bulk_g2s(dst, (prod_half ? vc_base : kc_base) + off, page_bytes, bar, policy);
       } else {
         bulk_g2s(dst, kc_base + off, page_bytes, bar, policy);
@@ -231,8 +243,8 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
       }
     }
     prod_slot = (prod_slot + 1 == NSLOT) ? 0 : prod_slot + 1;
-    if (split_kv) {
-      if (prod_half) ++prod_pg;
+    if constexpr (split_kv) {
+      prod_pg += prod_half;
       prod_half ^= 1;
     } else {
       ++prod_pg;
@@ -248,6 +260,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
   const float kv_o = kFp8 ? *p.v_scale : 1.f;
   const float qk_scale = p.scale * kLog2e * kv_qk;
   bool failed = false;
+  const bool has_alibi = p.alibi != nullptr;
 
   while (cur.valid && !failed) {
     const int hq0 = cur.kvh * p.group + cur.hg * TR::kHeadsPerItem;
@@ -286,7 +299,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const int hl = nt * 8 + 2 * c + j;
-        slope[nt][j] = (p.alibi != nullptr && hl < nheads) ? p.alibi[hq0 + hl] * kLog2e : 0.f;
+        slope[nt][j] = (has_alibi && hl < nheads) ? p.alibi[hq0 + hl] * kLog2e : 0.f;
       }
 
     float o[KS][GP][4];
@@ -324,7 +337,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
         for (int nt = 0; nt < GP; ++nt)
 #pragma unroll
           for (int i = 0; i < 4; ++i) s[t][nt][i] = s2[nt][i] = float(kZero);
-        if (t < ntiles) {
+        if (NT == 1 || t < ntiles) {
           const int tt = 16 * t;
           if constexpr (!kFp8) {
             const uint32_t kaddr =
@@ -376,7 +389,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
             for (int i = 0; i < 4; ++i) s[t][nt][i] += s2[nt][i];
         }
       }
-      if (split_kv) {
+      if constexpr (split_kv) {
         // the K slot is free: refill it while the softmax runs
         __syncwarp();
         cons_slot = (cons_slot + 1 == NSLOT) ? 0 : cons_slot + 1;
@@ -403,7 +416,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
           for (int j = 0; j < 2; ++j) {
             float v_lo = s[t][nt][j] * qk_scale;
             float v_hi = s[t][nt][2 + j] * qk_scale;
-            if (p.alibi != nullptr) {
+            if (has_alibi) {
               v_lo += slope[nt][j] * float(tok_lo - seq_len + 1);
               v_hi += slope[nt][j] * float(tok_hi - seq_len + 1);
             }
@@ -482,7 +495,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
       }
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
-        if (t < ntiles) {
+        if (NT == 1 || t < ntiles) {
           const int tt = 16 * t;
           uint32_t pf[GP][2];  // P^T as B operand
 #pragma unroll
@@ -659,7 +672,8 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
     cur = nxt;
     nxt = decode(nn_raw);
     nn_raw = fetch();
-    if (prod_sel == 1) prod_sel = 0; else prod_pg = 0;
+    // the producer either already works on the new `cur` (keep its state) or starts it now
+    if (prod_sel == 1) prod_sel = 0; else producer_take(cur);
     while (inflight < NSLOT && produce_one()) {}
   }
 

@@ -489,9 +489,8 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
     // the latency of HBM; measured on B200 the first matters more and a shallow ring (about
     // 100-130 KiB in flight per SM) beats a deep one.  Pages of 4 KiB and more get separate
     // K and V slots; smaller pages share one slot and one barrier per block.
-    // B200PA_TUNE_SPLIT / _WARPS / _STAGES override (STAGES = slots per warp).
-    int split_kv = page_bytes >= 4096 ? 1 : 0;
-    if (const char* e = getenv("B200PA_TUNE_SPLIT")) split_kv = atoi(e) != 0;
+    // B200PA_TUNE_WARPS / B200PA_TUNE_STAGES override (STAGES = slots per warp).
+    const int split_kv = page_bytes >= 4096 ? 1 : 0;  // same rule as in the kernel
     const size_t slot_bytes = split_kv ? page_bytes : 2 * page_bytes;
     const size_t min_slots = split_kv ? 2 : 1;
     int nwarps = int(std::min<size_t>(size_t(ki.max_warps), budget / (min_slots * slot_bytes)));
@@ -508,7 +507,6 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
                 a->block_size);
       return B200PA_EUNSUPPORTED;
     }
-    p.split_kv = split_kv;
     p.nstages = ns;
     unsigned* arrive = nullptr;
     p.status = device_status_ptr();
