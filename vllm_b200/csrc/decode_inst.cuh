@@ -15,11 +15,11 @@ struct DecodeKernelInfo {
   int max_warps;
 };
 
-// Warps per CTA the kernel is compiled for: 16 when the register budget allows
-// (<= 128 registers per thread), else 8.
+// Warps per CTA the kernel is compiled for, by its register footprint (accumulators and
+// query fragments grow with D * GP): 16 warps (<= 128 registers per thread), 12 (<= 168) or 8.
 template <int KV, int D, int GP>
 constexpr int decode_max_warps() {
-  return (D * GP <= 128) ? 16 : 8;
+  return (D * GP <= 128) ? 16 : (D * GP <= 256 ? 12 : 8);
 }
 
 template <typename QT, int KV, int D, int GP, int NT>
