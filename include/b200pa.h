@@ -117,9 +117,11 @@ typedef struct b200pa_attn_args {
   int32_t q_dtype;  /* b200pa_dtype    */
   int32_t kv_dtype; /* b200pa_kv_dtype */
 
-  /* Block-sparse arguments of the reference signature.  Only the dense case
-   * (blocksparse_vert_stride <= 1) is implemented; anything else returns
-   * B200PA_EUNSUPPORTED. */
+  /* Block-sparse arguments of the reference signature
+   * (attention_kernels.cuh:187-262): blocksparse_vert_stride <= 1 is dense
+   * attention; larger values keep the last blocksparse_local_blocks sparse
+   * blocks plus every vert_stride-th one (shifted per head by
+   * head_sliding_step).  The sparse case runs on the generic kernel. */
   int32_t tp_rank;
   int32_t blocksparse_local_blocks;
   int32_t blocksparse_vert_stride;

@@ -68,6 +68,141 @@ __device__ __forceinline__ int load_bt(const DecodeParams& p, const WorkItem& it
   return __ldg(p.block_tables + int64_t(it.seq) * p.max_blocks_per_seq + it.first_page + pg);
 }
 
+// Merges the split-KV partials of `nheads` consecutive heads of one sequence into `outp`
+// (the reference's paged_attention_v2_reduce_kernel, attention_kernels.cuh:559-664, for one
+// warp).  row0 = index of the first head's row in exp_sums / max_logits ([.., P] floats) and,
+// times D, in tmp_out.  Overwrites exp_sums with the normalised weights.  Kept out of line:
+// it runs once per sequence and kv head and must not cost the page loop any registers.
+template <typename QT, int D>
+__device__ __noinline__ void merge_partials(float* exp_sums, const float* max_logits,
+                                            const QT* tmp, QT* outp, int64_t row0, int np, int P,
+                                            int nheads, int lane) {
+  constexpr bool kOutBf = std::is_same_v<QT, __nv_bfloat16>;
+  // Phase 1: per head, turn (max logit, exp sum) of its partitions into normalised weights.
+  // Lanes run over partitions, four heads share one memory round trip.
+  for (int h0 = 0; h0 < nheads; h0 += 4) {
+    float ml0[4], es0[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const bool ok = h0 + k < nheads && lane < np;
+      const int64_t at = row0 + int64_t(ok ? h0 + k : h0) * P + (ok ? lane : 0);
+      ml0[k] = ok ? __ldcg(max_logits + at) : -INFINITY;
+      es0[k] = ok ? __ldcg(exp_sums + at) : 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (h0 + k >= nheads) break;  // warp-uniform
+      const float* ml = max_logits + row0 + int64_t(h0 + k) * P;
+      float* es = exp_sums + row0 + int64_t(h0 + k) * P;
+      float mx = ml0[k];
+      for (int j = lane + 32; j < np; j += 32) mx = fmaxf(mx, __ldcg(ml + j));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      const float w0 = lane < np ? es0[k] * fast_exp2(ml0[k] - mx) : 0.f;
+      float sum = w0;
+      for (int j = lane + 32; j < np; j += 32) {
+        const float w = __ldcg(es + j) * fast_exp2(__ldcg(ml + j) - mx);
+        es[j] = w;
+        sum += w;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      const float winv = __fdividef(1.f, sum + 1e-6f);
+      if (lane < np) es[lane] = w0 * winv;
+      for (int j = lane + 32; j < np; j += 32) es[j] *= winv;
+    }
+  }
+  __syncwarp();  // weights written by other lanes are read below
+  // Phase 2: out = sum_j weight_j * partial_j.  Work unit = 8 consecutive output elements
+  // (16 bytes) of one head; every load is independent of every other.
+  constexpr int UPH = D / 8;  // units per head
+  const int units = nheads * UPH;
+  auto fma8 = [&](float* acc, float w, const uint4& v) {
+    const uint32_t vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float f0, f1;
+      if constexpr (kOutBf) {
+        f0 = __uint_as_float(vv[i] << 16);
+        f1 = __uint_as_float(vv[i] & 0xffff0000u);
+      } else {
+        const __half2 h = *reinterpret_cast<const __half2*>(&vv[i]);
+        f0 = __low2float(h);
+        f1 = __high2float(h);
+      }
+      acc[2 * i] += w * f0;
+      acc[2 * i + 1] += w * f1;
+    }
+  };
+  auto store8 = [&](QT* dst, const float* acc) {
+    uint4 o4;
+    o4.x = pack2<kOutBf>(acc[0], acc[1]);
+    o4.y = pack2<kOutBf>(acc[2], acc[3]);
+    o4.z = pack2<kOutBf>(acc[4], acc[5]);
+    o4.w = pack2<kOutBf>(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(dst) = o4;
+  };
+  if (units <= 32) {
+    // few units: several lanes share a unit and split its partitions
+    int u2 = 1;
+    while (u2 < units) u2 <<= 1;
+    const int lpu = 32 / u2;  // lanes per unit
+    const int unit = lane & (u2 - 1);
+    const int sub = lane / u2;
+    const bool ok = unit < units;
+    const int uu = ok ? unit : 0;
+    const int hl = uu / UPH;
+    const int e0 = (uu % UPH) * 8;
+    const float* wt = exp_sums + row0 + int64_t(hl) * P;
+    const QT* src = tmp + (row0 + int64_t(hl) * P) * D + e0;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll 8
+    for (int j = sub; j < np; j += lpu) {
+      const float w = __ldcg(wt + j);
+      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src + int64_t(j) * D));
+      fma8(acc, w, v);
+    }
+    for (int o = u2; o < 32; o <<= 1) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
+    }
+    if (ok && sub == 0) store8(outp + hl * D + e0, acc);
+  } else {
+    // many units: a lane works on two of them at once
+    for (int u0 = lane; u0 < units; u0 += 64) {
+      const float* wt[2];
+      const QT* src[2];
+      float acc[2][8];
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int u = u0 + 32 * k < units ? u0 + 32 * k : u0;
+        const int hl = u / UPH;
+        const int e0 = (u % UPH) * 8;
+        wt[k] = exp_sums + row0 + int64_t(hl) * P;
+        src[k] = tmp + (row0 + int64_t(hl) * P) * D + e0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[k][i] = 0.f;
+      }
+#pragma unroll 8
+      for (int j = 0; j < np; ++j) {
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const float w = __ldcg(wt[k] + j);
+          const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src[k] + int64_t(j) * D));
+          fma8(acc[k], w, v);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int u = u0 + 32 * k;
+        if (u < units) store8(outp + (u / UPH) * D + (u % UPH) * 8, acc[k]);
+      }
+    }
+  }
+}
+
 template <typename QT, int KV, int D, int GP, int NT, int MAXW>
 __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodeParams p) {
   using TR = DecodeTraits<QT, KV, D, GP>;
@@ -147,7 +282,20 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
   const char* kc_base = static_cast<const char*>(p.kc);
   const char* vc_base = static_cast<const char*>(p.vc);
 
+  // Up to three items per resident warp: warp w of the grid owns items w, w + W, w + 2W
+  // (W = warps in the grid; numbered so that consecutive items land on different SMs).  No
+  // ticket round trips, and nobody holds a second item while another warp idles.  Larger
+  // launches pull tickets from the global counter, which balances items of unequal length.
+  const unsigned grid_warps = gridDim.x * unsigned(nwarps);
+  const bool strided = total_items <= 3u * grid_warps;
+  unsigned next_strided = unsigned(warp) * gridDim.x + blockIdx.x;
+
   auto fetch = [&]() -> unsigned {
+    if (strided) {
+      const unsigned v = next_strided;
+      next_strided += grid_warps;
+      return v;
+    }
     unsigned v = 0;
     if (lane == 0) v = atomicAdd(p.sched, 1u);
     return __shfl_sync(0xffffffffu, v, 0);
@@ -188,9 +336,25 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
     return it;
   };
 
-  WorkItem cur = decode(fetch());
-  WorkItem nxt = decode(fetch());
-  unsigned nn_raw = fetch();
+  // A warp always knows its current item, the next one (decoded, block ids loaded) and the
+  // number of the one after.  With tickets, the second and third are requested as soon as the
+  // first has arrived and their round trips overlap with the decoding of the first.
+  const unsigned raw0 = fetch();
+  unsigned raw1 = 0, raw2 = 0;
+  if (strided) {
+    raw1 = fetch();
+    raw2 = fetch();
+  } else if (lane == 0) {
+    raw1 = atomicAdd(p.sched, 1u);
+    raw2 = atomicAdd(p.sched, 1u);
+  }
+  WorkItem cur = decode(raw0);
+  if (!strided) {
+    raw1 = __shfl_sync(0xffffffffu, raw1, 0);
+    raw2 = __shfl_sync(0xffffffffu, raw2, 0);
+  }
+  WorkItem nxt = decode(raw1);
+  unsigned nn_raw = raw2;
 
   // ---- producer state.  The ring is filled in the order K(page 0), V(page 0), K(page 1), ...
   int prod_sel = 0;   // 0: producing pages of `cur`, 1: of `nxt`
@@ -614,57 +778,10 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
       if (old == unsigned(cur.nparts - 1)) {
         if (lane == 0) *cnt = 0;  // re-arm for the next launch
         __threadfence();          // order the loads below after the observed arrivals
-        const int np = cur.nparts;
-        const int P = p.max_partitions;
-        // Work unit = 8 consecutive output elements (16 bytes) of one head; lane takes
-        // units lane, lane+32, ...  All loads of a unit's partitions are independent, so
-        // the merge costs a couple of L2 round trips rather than one per partition.
-        constexpr int UPH = D / 8;  // units per head
-        const int units = nheads * UPH;
-        for (int u = lane; u < units; u += 32) {
-          const int hl = u / UPH;
-          const int e0 = (u % UPH) * 8;
-          const int64_t row = (int64_t(cur.seq) * p.num_heads + hq0 + hl) * P;
-          const float* ml = p.max_logits + row;
-          const float* es = p.exp_sums + row;
-          float mx = -INFINITY;
-#pragma unroll 4
-          for (int j = 0; j < np; ++j) mx = fmaxf(mx, __ldcg(ml + j));
-          float acc[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-          float wsum = 0.f;
-          const QT* src = static_cast<const QT*>(p.tmp_out) + row * D + e0;
-#pragma unroll 4
-          for (int j = 0; j < np; ++j) {
-            const float w = __ldcg(es + j) * fast_exp2(__ldcg(ml + j) - mx);
-            const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src + int64_t(j) * D));
-            wsum += w;
-            const uint32_t vv[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              float f0, f1;
-              if constexpr (kOutBf) {
-                f0 = __uint_as_float(vv[i] << 16);
-                f1 = __uint_as_float(vv[i] & 0xffff0000u);
-              } else {
-                const __half2 h = *reinterpret_cast<const __half2*>(&vv[i]);
-                f0 = __low2float(h);
-                f1 = __high2float(h);
-              }
-              acc[2 * i] += w * f0;
-              acc[2 * i + 1] += w * f1;
-            }
-          }
-          const float winv = __fdividef(1.f, wsum + 1e-6f);
-          uint4 o4;
-          o4.x = pack2<kOutBf>(acc[0] * winv, acc[1] * winv);
-          o4.y = pack2<kOutBf>(acc[2] * winv, acc[3] * winv);
-          o4.z = pack2<kOutBf>(acc[4] * winv, acc[5] * winv);
-          o4.w = pack2<kOutBf>(acc[6] * winv, acc[7] * winv);
-          *reinterpret_cast<uint4*>(static_cast<QT*>(p.out) +
-                                    (int64_t(cur.seq) * p.num_heads + hq0 + hl) * D + e0) = o4;
-        }
+        merge_partials<QT, D>(p.exp_sums, p.max_logits, static_cast<const QT*>(p.tmp_out),
+                              static_cast<QT*>(p.out) + (int64_t(cur.seq) * p.num_heads + hq0) * D,
+                              (int64_t(cur.seq) * p.num_heads + hq0) * p.max_partitions,
+                              cur.nparts, p.max_partitions, nheads, lane);
       }
     }
 

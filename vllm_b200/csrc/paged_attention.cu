@@ -444,25 +444,61 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
   if (fn != nullptr) {
     p.head_groups = (p.group + 8 * gp - 1) / (8 * gp);
     const size_t page_bytes = size_t(a->head_size) * a->block_size * es;
+    // Ring geometry.  Warps hide the latency of the per-page instruction chain, ring slots
+    // the latency of HBM; measured on B200 the first matters more and a shallow ring (about
+    // 100-130 KiB in flight per SM) beats a deep one when there is work for every warp.
+    // Pages of 4 KiB and more get separate K and V slots; smaller pages share one slot and
+    // one barrier per block.
+    const int split_kv = page_bytes >= 4096 ? 1 : 0;  // same rule as in the kernel
+    const size_t slot_bytes = split_kv ? page_bytes : 2 * page_bytes;
+    const size_t min_slots = split_kv ? 2 : 1;
+    const size_t budget_total = 227 * 1024 - 1024;  // static smem + slack
+    auto ring_budget = [&](bool with_table) {
+      const size_t table = with_table ? size_t((p.num_seqs + 1 + 3) & ~3) * 4 : 0;
+      return budget_total - std::min(budget_total - 2048, table) - 1024 /* mbarriers */;
+    };
+    auto warps_for = [&](size_t budget) {
+      int w = int(std::min<size_t>(size_t(ki.max_warps), budget / (min_slots * slot_bytes)));
+      if (es == 2 && w > 12) w = 12;  // 16-bit caches: 12 warps measured best
+      if (w >= 8) w &= ~3;            // same number of warps on each of the 4 schedulers
+      return std::max(w, 1);
+    };
     // The partition prefix table lives in shared memory; very large batches run
     // without it (one work item per sequence and kv head).
     if (a->max_seq_len > 64 && p.num_seqs <= 12000 && !getenv("B200PA_TUNE_NO_V1_SPLIT")) {
       // Split-KV into the library's own workspace when the caller gave no scratch (v1, or v2
       // with a single 512-token partition) or when the caller's 512-token partitions are too
-      // coarse to fill the GPU.  Partition size: 512 tokens, refined down to 64 while the
-      // batch still has fewer than ~4 work items per resident warp.
-      const int64_t warps_total = int64_t(sm_count()) * 12;
+      // coarse for the batch.  Two regimes, measured on B200:
+      //  - fewer work items than resident warps: the launch lasts as long as one item, so take
+      //    the finest partition that still gives every item its own warp;
+      //  - more: warps pull several items each and a few items per warp balance the load, so
+      //    refine while there are at most ~4 per warp.
+      // Either way the partitions of one (sequence, kv head) are merged by a single warp,
+      // which bounds how many are worth having (fewer when an item carries many heads).
+      const int64_t warps_total = int64_t(sm_count()) * warps_for(ring_budget(true));
       const int64_t units = int64_t(p.num_seqs) * p.num_kv_heads * p.head_groups;
+      const int heads_per_item = std::min(p.group, 8 * gp);
+      int max_parts = std::max(16, 64 / heads_per_item);
+      if (const char* e = getenv("B200PA_TUNE_MAX_PARTS")) max_parts = atoi(e);
+      auto parts_of = [&](int t) { return (int64_t(a->max_seq_len) + t - 1) / t; };
       int pt = kPartitionTokens;
-      while (pt > 64 && units * ((a->max_seq_len + pt / 2 - 1) / (pt / 2)) <= 4 * warps_total) pt /= 2;
-      if (!split || pt < kPartitionTokens) {
-        const int64_t parts = (int64_t(a->max_seq_len) + pt - 1) / pt;
-        const int64_t n = int64_t(p.num_seqs) * p.num_heads * parts;
+      const int64_t per_warp = units * parts_of(pt) <= warps_total ? 1 : 4;
+      while (pt > 64 && parts_of(pt / 2) <= max_parts &&
+             units * parts_of(pt / 2) <= per_warp * warps_total)
+        pt /= 2;
+      if (const char* e = getenv("B200PA_TUNE_PT")) pt = atoi(e);  // 0: no library split
+      if (pt > 0 && (!split || pt < kPartitionTokens)) {
         auto up = [](int64_t v) { return (v + 255) & ~int64_t(255); };
-        const int64_t stat = up(n * 4);
-        const int64_t need = 2 * stat + up(n * a->head_size * 2);
-        unsigned char* ws = (parts > 1 && need <= int64_t(kV1ScratchBytes) &&
-                             units <= kArrivePerRegion) ? v1_scratch_ptr() : nullptr;
+        auto need_of = [&](int t) {
+          const int64_t n = int64_t(p.num_seqs) * p.num_heads * parts_of(t);
+          return 2 * up(n * 4) + up(n * a->head_size * 2);
+        };
+        while (pt < kPartitionTokens && need_of(pt) > int64_t(kV1ScratchBytes)) pt *= 2;
+        const int64_t parts = parts_of(pt);
+        const int64_t stat = up(int64_t(p.num_seqs) * p.num_heads * parts * 4);
+        unsigned char* ws = ((!split || pt < kPartitionTokens) && parts > 1 &&
+                             need_of(pt) <= int64_t(kV1ScratchBytes) && units <= kArrivePerRegion)
+                                ? v1_scratch_ptr() : nullptr;
         if (ws != nullptr) {
           split = true;
           p.part_tokens = pt;
@@ -478,28 +514,32 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
     p.len_cap = split ? int(std::min<int64_t>(int64_t(p.max_partitions) * p.part_tokens, INT32_MAX))
                       : INT32_MAX;
     p.use_table = split ? 1 : 0;
-    size_t table_bytes = p.use_table ? size_t((p.num_seqs + 1 + 3) & ~3) * 4 : 0;
-    const size_t budget_total = 227 * 1024 - 1024;  // static smem + slack
+    const size_t table_bytes = p.use_table ? size_t((p.num_seqs + 1 + 3) & ~3) * 4 : 0;
     if (table_bytes > 48 * 1024) {
       set_error("num_seqs=%d is too large for the split-KV partition table", a->num_seqs);
       return B200PA_EUNSUPPORTED;
     }
-    const size_t budget = budget_total - table_bytes - 1024 /* mbarriers */;
-    // Ring geometry.  Warps hide the latency of the per-page instruction chain, ring slots
-    // the latency of HBM; measured on B200 the first matters more and a shallow ring (about
-    // 100-130 KiB in flight per SM) beats a deep one.  Pages of 4 KiB and more get separate
-    // K and V slots; smaller pages share one slot and one barrier per block.
+    const size_t budget = ring_budget(p.use_table != 0);
     // B200PA_TUNE_WARPS / B200PA_TUNE_STAGES override (STAGES = slots per warp).
-    const int split_kv = page_bytes >= 4096 ? 1 : 0;  // same rule as in the kernel
-    const size_t slot_bytes = split_kv ? page_bytes : 2 * page_bytes;
-    const size_t min_slots = split_kv ? 2 : 1;
-    int nwarps = int(std::min<size_t>(size_t(ki.max_warps), budget / (min_slots * slot_bytes)));
-    if (es == 2 && nwarps > 12) nwarps = 12;  // 16-bit caches: 12 warps measured best
-    if (nwarps >= 8) nwarps &= ~3;  // same number of warps on each of the 4 schedulers
-    if (nwarps < 1) nwarps = 1;
+    int nwarps = warps_for(budget);
     if (const char* e = getenv("B200PA_TUNE_WARPS"))
       nwarps = std::max(1, std::min(ki.max_warps, atoi(e)));
-    int ns = int(std::min<size_t>(split_kv ? 2 : 2, budget / (size_t(nwarps) * slot_bytes)));
+    // Launches with fewer work items than warps are bound by the latency of one item, not by
+    // bandwidth: run just enough warps to give every item its own (a multiple of 4, at least
+    // 4) and spend the shared memory on a deeper ring (<= 8 slots) so that one warp keeps
+    // many pages in flight.
+    int ns = 2;
+    {
+      const int64_t parts_ub =
+          split ? std::max<int64_t>(1, (int64_t(a->max_seq_len) + p.part_tokens - 1) / p.part_tokens) : 1;
+      const int64_t items_ub = int64_t(p.num_seqs) * p.num_kv_heads * p.head_groups * parts_ub;
+      if (items_ub <= int64_t(sm_count()) * nwarps && !getenv("B200PA_TUNE_WARPS")) {
+        const int need = int((items_ub + sm_count() - 1) / sm_count());
+        nwarps = std::min(nwarps, std::max(4, (need + 3) & ~3));
+        ns = 8;
+      }
+    }
+    ns = int(std::min<size_t>(size_t(ns), budget / (size_t(nwarps) * slot_bytes)));
     if (const char* e = getenv("B200PA_TUNE_STAGES"))
       ns = std::max(int(min_slots), std::min(int(budget / (size_t(nwarps) * slot_bytes)), atoi(e)));
     if (ns < int(min_slots)) {
