@@ -310,3 +310,61 @@ def test_lengths_beyond_max_seq_len_do_not_overrun_the_scratch():
     w.seq_lens = torch.clamp(w.seq_lens, max=1024)
     want = W.run_attention(w, version="v2")
     torch.testing.assert_close(out.float(), want.float(), atol=1e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("case", [
+    # (heads, kv heads, head size, lens, version): which part of the split-KV merge it reaches
+    (1, 1, 64, [4096], "v1"),          # one head of 8 units: lanes share units; 64 partitions
+    (8, 8, 128, [4000, 77], "v1"),     # single-head items, fine partitions
+    (16, 1, 256, [3000, 513, 1], "v2"),  # 16 heads per item (two n-tiles), 512 units per merge
+    (16, 1, 256, [3000, 513, 1], "v1"),
+    (12, 1, 80, [2500, 640], "v2"),    # ragged head group (12 of 16), 10 units per head
+    (4, 1, 128, [40000, 5], "v2"),     # more partitions than lanes
+])
+@pytest.mark.parametrize("kv", ["auto", "fp8"])
+def test_split_kv_merge_shapes(case, kv):
+    hq, hkv, d, lens, version = case
+    lens = np.array(lens)
+    rng = np.random.default_rng(21)
+    w = W.make_decode("merge", num_seqs=len(lens), num_heads=hq, num_kv_heads=hkv, head_size=d,
+                      block_size=16, lens=lens, dtype=torch.bfloat16, kv_cache_dtype=kv, device=DEV,
+                      seed=21, rng=rng)
+    w.query.mul_(8.0)
+    check(w, version)
+    # a second call on the same library workspace / scratch gives the same bits
+    a = W.run_attention(w, version=version).clone()
+    b = W.run_attention(w, version=version)
+    assert torch.equal(a, b)
+
+
+def _torch_fp32_reference(w):
+    """Plain fp32 attention over the gathered pages, on the GPU (16-bit caches only)."""
+    S, Hq, D = w.query.shape
+    Hkv, B = w.num_kv_heads, w.block_size
+    out = torch.empty(S, Hq, D, dtype=torch.float32, device=w.query.device)
+    for s in range(S):
+        n = int(w.seq_lens[s])
+        blocks = w.block_tables[s, :(n + B - 1) // B].long()
+        k = w.key_cache[blocks].permute(1, 0, 3, 2, 4).reshape(Hkv, -1, D)[:, :n].float()
+        v = w.value_cache[blocks].permute(1, 0, 3, 2).reshape(Hkv, -1, D)[:, :n].float()
+        q = w.query[s].float().view(Hkv, Hq // Hkv, D)
+        p = (torch.einsum("hgd,hld->hgl", q, k) * w.scale).softmax(-1)
+        out[s] = torch.einsum("hgl,hld->hgd", p, v).reshape(Hq, D)
+    return out
+
+
+@pytest.mark.parametrize("num_seqs", [40, 110])
+def test_items_per_warp_regimes(num_seqs):
+    """Between one and three work items per resident warp the kernel deals items out by a fixed
+    stride, beyond that through its ticket counter; both must cover every item exactly once."""
+    rng = np.random.default_rng(5)
+    lens = rng.integers(3500, 4097, size=num_seqs)
+    lens[0] = 4096
+    w = W.make_decode("regime", num_seqs=num_seqs, num_heads=32, num_kv_heads=8, head_size=64,
+                      block_size=16, lens=lens, dtype=torch.bfloat16, kv_cache_dtype="auto", device=DEV,
+                      seed=5, rng=rng)
+    w.query.mul_(8.0)
+    check(w, "v2", seqs=[0, 1, num_seqs // 2, num_seqs - 1])
+    # every sequence, against plain fp32 attention
+    got = W.run_attention(w, version="v2").float()
+    torch.testing.assert_close(got, _torch_fp32_reference(w), atol=1e-2, rtol=1e-2)
