@@ -13,6 +13,7 @@ using DecodeLaunchFn = cudaError_t (*)(const DecodeParams&, int grid, int thread
 struct DecodeKernelInfo {
   DecodeLaunchFn fn;
   int max_warps;
+  int pages_per_step;  // cache blocks per pipeline step (sizes the ring slots)
 };
 
 // Warps per CTA the kernel is compiled for, by its register footprint (accumulators and
@@ -50,8 +51,12 @@ cudaError_t decode_launch(const DecodeParams& p, int grid, int threads, size_t s
 
 template <typename QT, int KV, int D, int GP>
 DecodeKernelInfo pick_nt(int nt) {
-  if (nt == 1) return {decode_launch<QT, KV, D, GP, 1>, decode_max_warps<KV, D, GP>()};
-  return {decode_launch<QT, KV, D, GP, 2>, decode_max_warps<KV, D, GP>()};
+  constexpr int es = KV == kCache16 ? 2 : 1;
+  if (nt == 1)
+    return {decode_launch<QT, KV, D, GP, 1>, decode_max_warps<KV, D, GP>(),
+            decode_pages_per_step(es, D, 1)};
+  return {decode_launch<QT, KV, D, GP, 2>, decode_max_warps<KV, D, GP>(),
+          decode_pages_per_step(es, D, 2)};
 }
 
 template <typename QT, int KV, int D>
@@ -67,16 +72,16 @@ DecodeKernelInfo pick_kv(int kv_dtype, int gp, int nt) {
     case B200PA_KV_FP8_E4M3: return pick_gp<QT, kCacheE4M3, D>(gp, nt);
     case B200PA_KV_FP8_E5M2: return pick_gp<QT, kCacheE5M2, D>(gp, nt);
   }
-  return {nullptr, 0};
+  return {nullptr, 0, 1};
 }
 
 // gp: 8-head n-tiles per work item (1 or 2); nt: 16-token tiles per cache block (1 or 2).
 template <int D>
 DecodeKernelInfo find_decode_for(int q_dtype, int kv_dtype, int gp, int nt) {
-  if ((gp != 1 && gp != 2) || (nt != 1 && nt != 2)) return {nullptr, 0};
+  if ((gp != 1 && gp != 2) || (nt != 1 && nt != 2)) return {nullptr, 0, 1};
   if (q_dtype == B200PA_BF16) return pick_kv<__nv_bfloat16, D>(kv_dtype, gp, nt);
   if (q_dtype == B200PA_F16) return pick_kv<__half, D>(kv_dtype, gp, nt);
-  return {nullptr, 0};
+  return {nullptr, 0, 1};
 }
 
 // One finder per translation unit (defined in decode_d*.cu).

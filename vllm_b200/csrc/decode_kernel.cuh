@@ -37,6 +37,13 @@ namespace b200pa {
 
 enum : int { kCache16 = 0, kCacheE4M3 = 1, kCacheE5M2 = 2 };
 
+// Cache blocks per pipeline step of the decode kernel: 2 for 16-token blocks whose K page is
+// at most 1 KiB, else 1 (measured: pairing 1 KiB pages gains 6-9 %, pairing 2 KiB pages loses
+// 1-5 %).  esize = bytes per cache element, bt = 16-token tiles per block.
+constexpr int decode_pages_per_step(int esize, int d, int bt) {
+  return (bt == 1 && d * 16 * esize <= 1024) ? 2 : 1;
+}
+
 struct WorkItem {
   int seq;
   int kvh;
@@ -203,7 +210,7 @@ __device__ __noinline__ void merge_partials(float* exp_sums, const float* max_lo
   }
 }
 
-template <typename QT, int KV, int D, int GP, int NT, int MAXW>
+template <typename QT, int KV, int D, int GP, int BT, int MAXW>
 __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodeParams p) {
   using TR = DecodeTraits<QT, KV, D, GP>;
   constexpr bool kFp8 = TR::kFp8;
@@ -219,14 +226,20 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
   const int nwarps = blockDim.x >> 5;
   const int g = lane >> 2;  // fragment row group
   const int c = lane & 3;   // fragment column pair
-  constexpr int B = 16 * NT;  // tokens per cache block (16 or 32)
+  constexpr int B = 16 * BT;  // tokens per cache block (16 or 32)
+  // One pipeline step covers PP consecutive blocks of the sequence: two when blocks are very
+  // small, so that barrier traffic, softmax bookkeeping and producer run once per 32 tokens.
+  constexpr int PP = decode_pages_per_step(KV != kCache16 ? 1 : 2, D, BT);
+  constexpr int NT = BT * PP;  // 16-token tiles per step
+  constexpr int ST = 16 * NT;  // tokens per step
   constexpr uint32_t page_bytes = uint32_t(D) * B * (KV != kCache16 ? 1 : 2);
+  constexpr uint32_t step_bytes = PP * page_bytes;  // K (or V) bytes of one step
   const int NSLOT = p.nstages;  // ring slots of this warp
-  // Pages of 4 KiB and more get one slot and one barrier each for K and V (finer prefetch
-  // granularity: the K slot is refilled while the softmax runs); smaller pages share one slot
-  // and one barrier per block (half the barrier traffic).  The host uses the same rule.
-  constexpr bool split_kv = page_bytes >= 4096;
-  constexpr uint32_t slot_bytes = split_kv ? page_bytes : 2 * page_bytes;
+  // Steps of 4 KiB and more get one slot and one barrier each for K and V (finer prefetch
+  // granularity: the K slot is refilled while the softmax runs); smaller ones share one slot
+  // and one barrier (half the barrier traffic).  The host uses the same rule.
+  constexpr bool split_kv = step_bytes >= 4096;
+  constexpr uint32_t slot_bytes = split_kv ? step_bytes : 2 * step_bytes;
   const int PT = p.part_tokens;  // tokens per split-KV partition (a multiple of the block size)
 
   // ---- shared memory carve-up: [partition prefix table][mbarriers][stages]
@@ -360,7 +373,8 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
   int prod_sel = 0;   // 0: producing pages of `cur`, 1: of `nxt`
   int prod_pg = 0;
   int prod_half = 0;  // 0: the K page is next, 1: the V page of the same block
-  int prod_blk = 0;
+  int prod_blk[PP] = {};  // block ids of the step being requested
+  int prod_n = 0;         // blocks in that step (the last step of an item may be short)
   int prod_slot = 0;
   int inflight = 0;
   int cons_slot = 0;
@@ -392,26 +406,35 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
         pi_win = win;
         pi_bt = load_bt(p, prod_sel ? nxt : cur, win, lane);
       }
-      prod_blk = __shfl_sync(0xffffffffu, pi_bt, prod_pg & 31);
+      // items start on an even page and a window holds 32: both ids are in this window
+#pragma unroll
+      for (int i = 0; i < PP; ++i) prod_blk[i] = __shfl_sync(0xffffffffu, pi_bt, (prod_pg + i) & 31);
+      prod_n = min(PP, pi_npages - prod_pg);
     }
     if (lane == 0) {
-      const int64_t off = int64_t(prod_blk) * blk_stride_bytes + pi_kvoff;
       const uint32_t bar = my_bar0 + prod_slot * 8;
       const uint32_t dst = my_slot0 + prod_slot * slot_bytes;
-      mbar_expect_tx(bar, slot_bytes);
-      if constexpr (split_kv) {
-        bulk_g2s(dst, (prod_half ? vc_base : kc_base) + off, page_bytes, bar, policy);
-      } else {
-        bulk_g2s(dst, kc_base + off, page_bytes, bar, policy);
-        bulk_g2s(dst + page_bytes, vc_base + off, page_bytes, bar, policy);
+      mbar_expect_tx(bar, (split_kv ? 1u : 2u) * uint32_t(prod_n) * page_bytes);
+#pragma unroll
+      for (int i = 0; i < PP; ++i) {
+        if (i < prod_n) {
+          const int64_t off = int64_t(prod_blk[i]) * blk_stride_bytes + pi_kvoff;
+          if constexpr (split_kv) {
+            bulk_g2s(dst + i * page_bytes, (prod_half ? vc_base : kc_base) + off, page_bytes, bar,
+                     policy);
+          } else {
+            bulk_g2s(dst + i * page_bytes, kc_base + off, page_bytes, bar, policy);
+            bulk_g2s(dst + step_bytes + i * page_bytes, vc_base + off, page_bytes, bar, policy);
+          }
+        }
       }
     }
     prod_slot = (prod_slot + 1 == NSLOT) ? 0 : prod_slot + 1;
     if constexpr (split_kv) {
-      prod_pg += prod_half;
+      prod_pg += PP * prod_half;
       prod_half ^= 1;
     } else {
-      ++prod_pg;
+      prod_pg += PP;
     }
     ++inflight;
     return true;
@@ -480,9 +503,10 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
       l_run[nt][0] = l_run[nt][1] = 0.f;
     }
 
-    for (int pg = 0; pg < cur.npages; ++pg) {
-      const int page_tok0 = (cur.first_page + pg) * B;
-      // tiles of this page that hold at least one valid token (warp-uniform)
+    const int nsteps = (cur.npages + PP - 1) / PP;
+    for (int st = 0; st < nsteps; ++st) {
+      const int page_tok0 = (cur.first_page + st * PP) * B;  // first token of the step
+      // tiles of this step that hold at least one valid token (warp-uniform)
       const int ntiles = min(NT, (cur.tok_end - page_tok0 + 15) >> 4);
 
       // ================= K half: S^T = K . Q^T for every tile of the page
@@ -502,10 +526,11 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
 #pragma unroll
           for (int i = 0; i < 4; ++i) s[t][nt][i] = s2[nt][i] = float(kZero);
         if (NT == 1 || t < ntiles) {
-          const int tt = 16 * t;
+          const int tt = 16 * (t % BT);                        // tile's first token in its block
+          const uint32_t skt = sk + (t / BT) * page_bytes;     // that block's K page
           if constexpr (!kFp8) {
             const uint32_t kaddr =
-                sk + uint32_t(((lane >> 4) * B + tt + ((lane >> 3) & 1) * 8 + (lane & 7)) * 16);
+                skt + uint32_t(((lane >> 4) * B + tt + ((lane >> 3) & 1) * 8 + (lane & 7)) * 16);
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {
               uint32_t a0, a1, a2, a3;
@@ -520,7 +545,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
             // A row rho of half h <-> token 4*(rho/2) + 2*h + rho%2
             const int rho = lane & 7, hsel = (lane >> 3) & 1;
             const int tok = 4 * (rho >> 1) + 2 * hsel + (rho & 1);
-            const uint32_t kaddr = sk + uint32_t(((lane >> 4) * B + tt + tok) * 16);
+            const uint32_t kaddr = skt + uint32_t(((lane >> 4) * B + tt + tok) * 16);
 #pragma unroll
             for (int ks = 0; ks + 1 < KS; ks += 2) {
               uint32_t r0, r1, r2, r3, a0, a1, a2, a3, b0, b1, b2, b3;
@@ -539,7 +564,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
               constexpr int ks = KS - 1;
               uint32_t r0, r1, a0, a1, a2, a3;
               // lanes 0-15 supply the addresses of the two matrices (lanes 16-31 ignored)
-              ldsm_x2(sk + uint32_t((ks * B + tt + tok) * 16), r0, r1);
+              ldsm_x2(skt + uint32_t((ks * B + tt + tok) * 16), r0, r1);
               fp8x4_to_f16<kE5>(r0, a0, a2);
               fp8x4_to_f16<kE5>(r1, a1, a3);
 #pragma unroll
@@ -563,7 +588,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
       }
 
       // ================= scale, ALiBi, mask; online softmax over the whole page
-      const bool need_mask = page_tok0 + B > cur.tok_end;
+      const bool need_mask = page_tok0 + ST > cur.tok_end;
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
         int tok_lo, tok_hi;  // absolute token of accumulator rows g and g+8
@@ -641,17 +666,20 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
         failed = true;
         break;
       }
-      const uint32_t sv = my_slot0 + cons_slot * slot_bytes + (split_kv ? 0u : page_bytes);
+      const uint32_t sv = my_slot0 + cons_slot * slot_bytes + (split_kv ? 0u : step_bytes);
       // zero V columns of tokens past the end of the sequence (stale cache bytes
-      // could be NaN/Inf; the reference zeroes them too, attention_kernels.cuh:415-425)
+      // could be NaN/Inf; the reference zeroes them too, attention_kernels.cuh:415-425).
+      // Only the block holding the last valid token needs it: tiles beyond are skipped.
       if (need_mask) {
-        const int rem = cur.tok_end - page_tok0;
-        const int w = B - rem;
+        const int rem = cur.tok_end - page_tok0;  // valid tokens of this step, 1 .. ST-1
+        const int pl = (rem - 1) / B;             // block of the step that holds the last one
+        const int r = rem - pl * B;               // valid tokens in that block
+        const int w = B - r;
         unsigned char* vpage = slots + (size_t(warp) * NSLOT + cons_slot) * slot_bytes +
-                               (split_kv ? 0u : page_bytes);
+                               (split_kv ? 0u : step_bytes) + pl * page_bytes;
         for (int idx = lane; idx < D * w; idx += 32) {
           const int d = idx / w;
-          const int tk = rem + idx % w;
+          const int tk = r + idx % w;
           if constexpr (ES == 1) vpage[d * B + tk] = 0;
           else reinterpret_cast<uint16_t*>(vpage)[d * B + tk] = 0;
         }
@@ -660,7 +688,8 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
         if (NT == 1 || t < ntiles) {
-          const int tt = 16 * t;
+          const int tt = 16 * (t % BT);
+          const uint32_t svt = sv + (t / BT) * page_bytes;
           uint32_t pf[GP][2];  // P^T as B operand
 #pragma unroll
           for (int nt = 0; nt < GP; ++nt) {
@@ -669,7 +698,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
           }
           if constexpr (!kFp8) {
             const uint32_t vaddr =
-                sv + uint32_t(((((lane >> 3) & 1) * 8 + (lane & 7)) * B + tt + (lane >> 4) * 8) * 2);
+                svt + uint32_t(((((lane >> 3) & 1) * 8 + (lane & 7)) * B + tt + (lane >> 4) * 8) * 2);
 #pragma unroll
             for (int mt = 0; mt < KS; ++mt) {
               uint32_t a0, a1, a2, a3;
@@ -680,7 +709,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
             }
           } else {
             const uint32_t vaddr =
-                sv + uint32_t((16 * (lane >> 4) + ((lane >> 3) & 1) * 8 + (lane & 7)) * B + tt);
+                svt + uint32_t((16 * (lane >> 4) + ((lane >> 3) & 1) * 8 + (lane & 7)) * B + tt);
 #pragma unroll
             for (int mt = 0; mt + 1 < KS; mt += 2) {
               uint32_t r0, r1, r2, r3, a0, a1, a2, a3, b0, b1, b2, b3;
@@ -698,7 +727,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
             if constexpr (KS & 1) {
               constexpr int mt = KS - 1;
               uint32_t r0, r1, a0, a1, a2, a3;
-              ldsm_x2(sv + uint32_t((16 * mt + ((lane >> 3) & 1) * 8 + (lane & 7)) * B + tt), r0, r1);
+              ldsm_x2(svt + uint32_t((16 * mt + ((lane >> 3) & 1) * 8 + (lane & 7)) * B + tt), r0, r1);
               fp8x4_to_f16<kE5>(r0, a0, a2);
               fp8x4_to_f16<kE5>(r1, a1, a3);
 #pragma unroll

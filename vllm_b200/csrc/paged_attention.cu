@@ -285,7 +285,7 @@ static DecodeKernelInfo find_decode(int d, int qdt, int kv, int gp, int nt) {
     case 192: return find_decode_d192(qdt, kv, gp, nt);
     case 256: return find_decode_d256(qdt, kv, gp, nt);
   }
-  return {nullptr, 0};
+  return {nullptr, 0, 1};
 }
 
 template <typename QT>
@@ -428,7 +428,7 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
   const int es = a->kv_dtype == B200PA_KV_AUTO ? 2 : 1;
   auto aligned = [](const void* ptr, uintptr_t n) { return reinterpret_cast<uintptr_t>(ptr) % n == 0; };
   const int gp = p.group <= 8 ? 1 : 2;
-  DecodeKernelInfo ki{nullptr, 0};
+  DecodeKernelInfo ki{nullptr, 0, 1};
   // block-sparse attention (unused by any in-tree caller of the reference) runs on the
   // generic kernel only
   bool fast = !force_generic() && !sparse && a->q_dtype != B200PA_F32 &&
@@ -447,10 +447,11 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
     // Ring geometry.  Warps hide the latency of the per-page instruction chain, ring slots
     // the latency of HBM; measured on B200 the first matters more and a shallow ring (about
     // 100-130 KiB in flight per SM) beats a deep one when there is work for every warp.
-    // Pages of 4 KiB and more get separate K and V slots; smaller pages share one slot and
-    // one barrier per block.
-    const int split_kv = page_bytes >= 4096 ? 1 : 0;  // same rule as in the kernel
-    const size_t slot_bytes = split_kv ? page_bytes : 2 * page_bytes;
+    // A pipeline step is one cache block, or two when blocks are small.  Steps of 4 KiB and
+    // more get separate K and V slots; smaller ones share one slot and one barrier.
+    const size_t step_bytes = page_bytes * ki.pages_per_step;  // K (or V) bytes per pipeline step
+    const int split_kv = step_bytes >= 4096 ? 1 : 0;           // same rule as in the kernel
+    const size_t slot_bytes = split_kv ? step_bytes : 2 * step_bytes;
     const size_t min_slots = split_kv ? 2 : 1;
     const size_t budget_total = 227 * 1024 - 1024;  // static smem + slack
     auto ring_budget = [&](bool with_table) {
