@@ -154,7 +154,11 @@ def test_fp8_quantiser_fp32_inputs_ties_and_odd_scales():
     x_rand = rand_bits.view(torch.float32)
     x_norm = torch.randn(n, generator=g) * 3
     scales = [1.0, 0.011826, 3.7, 1 / 3, 5.3 / 448, 2.0 ** -20, 1.0000001, 0.9999999, 123456.7,
-              float(torch.rand(1, generator=g)) + 1e-3]
+              float(torch.rand(1, generator=g)) + 1e-3,
+              # significand of all ones, and both sides of the range in which the kernel replaces
+              # the division by reciprocal + residual corrections; a denormal scale
+              1.9999999, 1.9999999 * 2.0 ** -30, 2.0 ** -60, 2.0 ** -61, 2.0 ** 60, 2.0 ** 61,
+              1e-38, 1e-40, 3e38]
     for kv in ("fp8", "fp8_e5m2"):
         dt, fmax = O.FP8_FORMATS[kv]
         # every finite fp8 value and the midpoints between neighbours, times the scale, +- a few ulps

@@ -13,20 +13,94 @@
 //     in consecutive slots with the widest aligned store, instead of one
 //     1-2 byte store per element.
 //   * flash layout: 16-byte vector row copies, NHD or HND by strides.
-// Quantisation is cvt.rn.satfinite of an IEEE fp32 division, bit-identical to
-// the reference's scaled_convert (quant_utils.cuh:469-502).
+// Quantisation is cvt.rn.satfinite of the correctly rounded fp32 quotient x / scale,
+// bit-identical to the reference's scaled_convert (quant_utils.cuh:469-502).
 #include "common.cuh"
 
 namespace b200pa {
 
 enum : int { kKvAuto = 0, kKvE4M3 = 1, kKvE5M2 = 2 };
 
+// x / scale, correctly rounded, for one scale and many x.  The compiler's division spends a
+// MUFU.RCP, a range check and a slow-path branch on every element, which made the KV write
+// XU-bound; here the reciprocal is taken once and each quotient is the product x * r followed
+// by two residual corrections q += fma(-q, s, x) * r.  The first leaves q within one ulp, the
+// second then yields the correctly rounded quotient (Markstein's theorem; r is the correctly
+// rounded reciprocal).  Only used while nothing can overflow or lose residual bits to
+// underflow: scales within 2^+-60 and 2^-20 <= |q| < 2^17.  Outside that window the plain
+// product x * r is returned: larger quotients saturate in both fp8 formats and smaller ones
+// round to zero whatever their last bits are (the product also keeps the sign of a zero and
+// passes inf / NaN through, which the corrections would not).  Other scales use the division.
+struct ScaledDiv {
+  float s, r;
+  bool fast;
+  __device__ __forceinline__ explicit ScaledDiv(float scale) : s(scale) {
+    r = __fdiv_rn(1.f, scale);
+    const float a = fabsf(scale);
+    fast = a >= 0x1p-60f && a <= 0x1p60f;
+  }
+  // Two quotients at once on the packed fp32 pipe (fma.rn.f32x2, sm_100).
+  __device__ __forceinline__ void pair(float x0, float x1, float& o0, float& o1) const {
+    if (!fast) {
+      o0 = __fdiv_rn(x0, s);
+      o1 = __fdiv_rn(x1, s);
+      return;
+    }
+    float p0, p1, c0, c1;
+    asm("{\n"
+        " .reg .b64 x, r, ns, q, e;\n"
+        " mov.b64 x, {%4, %5};\n"
+        " mov.b64 r, {%6, %6};\n"
+        " mov.b64 ns, {%7, %7};\n"
+        " mul.rn.f32x2 q, x, r;\n"
+        " mov.b64 {%0, %1}, q;\n"
+        " fma.rn.f32x2 e, q, ns, x;\n"
+        " fma.rn.f32x2 q, e, r, q;\n"
+        " fma.rn.f32x2 e, q, ns, x;\n"
+        " fma.rn.f32x2 q, e, r, q;\n"
+        " mov.b64 {%2, %3}, q;\n"
+        "}"
+        : "=f"(p0), "=f"(p1), "=f"(c0), "=f"(c1)
+        : "f"(x0), "f"(x1), "f"(r), "f"(-s));
+    const float a0 = fabsf(p0), a1 = fabsf(p1);
+    o0 = (a0 >= 0x1p-20f && a0 < 0x1p17f) ? c0 : p0;
+    o1 = (a1 >= 0x1p-20f && a1 < 0x1p17f) ? c1 : p1;
+  }
+  __device__ __forceinline__ float operator()(float x) const {
+    if (!fast) return __fdiv_rn(x, s);
+    const float q0 = x * r;
+    float q = fmaf(fmaf(-q0, s, x), r, q0);
+    q = fmaf(fmaf(-q, s, x), r, q);
+    const float a = fabsf(q0);
+    return (a >= 0x1p-20f && a < 0x1p17f) ? q : q0;
+  }
+};
+
 template <typename in_t, typename cache_t, int KV>
-__device__ __forceinline__ cache_t store_convert(in_t v, float scale) {
+__device__ __forceinline__ cache_t store_convert(in_t v, const ScaledDiv& div) {
   if constexpr (KV == kKvAuto) {
     return v;
   } else {
-    return f32_to_fp8<KV == kKvE5M2>(__fdiv_rn(to_f32(v), scale));
+    return f32_to_fp8<KV == kKvE5M2>(div(to_f32(v)));
+  }
+}
+
+// N consecutive elements; fp8 conversions go two at a time (one cvt for a byte pair).
+template <typename in_t, typename cache_t, int KV, int N>
+__device__ __forceinline__ void convert_n(const in_t (&in)[N], cache_t* out, const ScaledDiv& div) {
+  if constexpr (KV == kKvAuto) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) out[i] = in[i];
+  } else {
+    static_assert(N % 2 == 0, "pairs");
+#pragma unroll
+    for (int i = 0; i < N; i += 2) {
+      float q0, q1;
+      div.pair(to_f32(in[i]), to_f32(in[i + 1]), q0, q1);
+      const uint16_t two = f32x2_to_fp8x2<KV == kKvE5M2>(q0, q1);
+      out[i] = static_cast<cache_t>(two & 0xFF);
+      out[i + 1] = static_cast<cache_t>(two >> 8);
+    }
   }
 }
 
@@ -75,8 +149,8 @@ reshape_and_cache_kernel(const in_t* __restrict__ key, const in_t* __restrict__ 
     s_slot[threadIdx.x] = threadIdx.x < ntok ? slot_mapping[tok0 + threadIdx.x] : int64_t(-1);
   __syncthreads();
 
-  const float k_scale = (KV == kKvAuto) ? 1.f : *k_scale_ptr;
-  const float v_scale = (KV == kKvAuto) ? 1.f : *v_scale_ptr;
+  const ScaledDiv k_scale((KV == kKvAuto) ? 1.f : *k_scale_ptr);
+  const ScaledDiv v_scale((KV == kKvAuto) ? 1.f : *v_scale_ptr);
   const int chunks = head_size / x;  // per head
   const int hd = num_heads * head_size;
   // 16-byte loads from key/value rows are legal when bases and row strides are 16-byte multiples
@@ -102,7 +176,7 @@ reshape_and_cache_kernel(const in_t* __restrict__ key, const in_t* __restrict__ 
     if (x * int(sizeof(cache_t)) == 16 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
       constexpr int N = 16 / sizeof(cache_t);        // elements per 16-byte store
       constexpr int L = N * sizeof(in_t) / 16;       // 16-byte loads that feed it
-      in_t in[N];
+      __align__(16) in_t in[N];
       if (in_vec_ok) {
 #pragma unroll
         for (int i = 0; i < L; ++i)
@@ -111,9 +185,8 @@ reshape_and_cache_kernel(const in_t* __restrict__ key, const in_t* __restrict__ 
 #pragma unroll
         for (int i = 0; i < N; ++i) in[i] = src[i];
       }
-      cache_t vals[N];
-#pragma unroll
-      for (int i = 0; i < N; ++i) vals[i] = store_convert<in_t, cache_t, KV>(in[i], k_scale);
+      __align__(16) cache_t vals[N];
+      convert_n<in_t, cache_t, KV, N>(in, vals, k_scale);
       *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(vals);
     } else {
       for (int i = 0; i < x; ++i) dst[i] = store_convert<in_t, cache_t, KV>(src[i], k_scale);
@@ -142,13 +215,18 @@ reshape_and_cache_kernel(const in_t* __restrict__ key, const in_t* __restrict__ 
     for (int gidx = threadIdx.x; gidx < groups; gidx += blockDim.x) {
       const int row0 = gidx * VD;  // (head, d) flattened; a group never straddles a head
       const in_t* src = value + int64_t(tok0) * value_stride + row0;
-      cache_t vals[VD][kTokTile];
+      __align__(16) cache_t vals[VD][kTokTile];
 #pragma unroll
-      for (int t = 0; t < kTokTile; ++t) {
-        in_t in[VD];
-        *reinterpret_cast<uint4*>(in) = *reinterpret_cast<const uint4*>(src + int64_t(t) * value_stride);
+      for (int t = 0; t < kTokTile; t += 2) {
+        __align__(16) in_t in0[VD], in1[VD];
+        *reinterpret_cast<uint4*>(in0) = *reinterpret_cast<const uint4*>(src + int64_t(t) * value_stride);
+        *reinterpret_cast<uint4*>(in1) =
+            *reinterpret_cast<const uint4*>(src + int64_t(t + 1) * value_stride);
 #pragma unroll
-        for (int d = 0; d < VD; ++d) vals[d][t] = store_convert<in_t, cache_t, KV>(in[d], v_scale);
+        for (int d = 0; d < VD; ++d) {
+          const in_t two[2] = {in0[d], in1[d]};
+          convert_n<in_t, cache_t, KV, 2>(two, &vals[d][t], v_scale);
+        }
       }
       cache_t* dst = value_cache + (b * hd + row0) * int64_t(block_size) + off;
 #pragma unroll
@@ -216,19 +294,24 @@ reshape_and_cache_flash_kernel(const in_t* __restrict__ key, const in_t* __restr
   if (vec_ok) {
     const int vec_per_head = head_size / VEC;
     const int items = num_heads * vec_per_head;
+    // a thread's items are K first, then V: the divider is set up once per tensor it touches
+    ScaledDiv scale(k_scale);
+    bool scale_is_v = false;
     for (int it = threadIdx.x; it < 2 * items; it += blockDim.x) {
       const bool is_v = it >= items;
+      if (is_v && !scale_is_v) {
+        scale = ScaledDiv(v_scale);
+        scale_is_v = true;
+      }
       const int j = is_v ? it - items : it;
       const int h = j / vec_per_head;
       const int e = (j % vec_per_head) * VEC;
       const in_t* s = (is_v ? vsrc : ksrc) + h * head_size + e;
       cache_t* d = (is_v ? vdst : kdst) + h * head_stride + e;
-      const float scale = is_v ? v_scale : k_scale;
-      in_t in[VEC];
+      __align__(16) in_t in[VEC];
       *reinterpret_cast<uint4*>(in) = *reinterpret_cast<const uint4*>(s);
-      cache_t outv[VEC];
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) outv[i] = store_convert<in_t, cache_t, KV>(in[i], scale);
+      __align__(16) cache_t outv[VEC];
+      convert_n<in_t, cache_t, KV, VEC>(in, outv, scale);
       if constexpr (sizeof(cache_t) * VEC == 16) {
         *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(outv);
       } else if constexpr (sizeof(cache_t) * VEC == 8) {
@@ -239,11 +322,12 @@ reshape_and_cache_flash_kernel(const in_t* __restrict__ key, const in_t* __restr
     }
   } else {
     const int items = num_heads * head_size;
+    const ScaledDiv kdiv(k_scale), vdiv(v_scale);
     for (int it = threadIdx.x; it < items; it += blockDim.x) {
       const int h = it / head_size;
       const int e = it % head_size;
-      kdst[h * head_stride + e] = store_convert<in_t, cache_t, KV>(ksrc[it], k_scale);
-      vdst[h * head_stride + e] = store_convert<in_t, cache_t, KV>(vsrc[it], v_scale);
+      kdst[h * head_stride + e] = store_convert<in_t, cache_t, KV>(ksrc[it], kdiv);
+      vdst[h * head_stride + e] = store_convert<in_t, cache_t, KV>(vsrc[it], vdiv);
     }
   }
 }
@@ -253,10 +337,11 @@ template <typename wide_t, bool kE5M2, bool kToFp8>
 __global__ void convert_fp8_kernel(void* __restrict__ dst_, const void* __restrict__ src_,
                                    int64_t numel, float scale) {
   const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  const ScaledDiv div(scale);
   for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < numel; i += stride) {
     if constexpr (kToFp8) {
       const wide_t v = static_cast<const wide_t*>(src_)[i];
-      static_cast<uint8_t*>(dst_)[i] = f32_to_fp8<kE5M2>(__fdiv_rn(to_f32(v), scale));
+      static_cast<uint8_t*>(dst_)[i] = f32_to_fp8<kE5M2>(div(to_f32(v)));
     } else {
       // reference order (quant_utils.cuh:360-372): fp8 -> half -> float * scale -> wide
       const uint8_t v = static_cast<const uint8_t*>(src_)[i];
