@@ -40,12 +40,8 @@ struct ScaledDiv {
     fast = a >= 0x1p-60f && a <= 0x1p60f;
   }
   // Two quotients at once on the packed fp32 pipe (fma.rn.f32x2, sm_100).
+  // Callers check `fast` once per kernel, not per pair.
   __device__ __forceinline__ void pair(float x0, float x1, float& o0, float& o1) const {
-    if (!fast) {
-      o0 = __fdiv_rn(x0, s);
-      o1 = __fdiv_rn(x1, s);
-      return;
-    }
     float p0, p1, c0, c1;
     asm("{\n"
         " .reg .b64 x, r, ns, q, e;\n"
@@ -133,6 +129,77 @@ __device__ __forceinline__ void store_run(cache_t* dst, const cache_t (&vals)[N]
   }
 }
 
+// n / d for small operands (n * d < 2^32) by one multiply-high with a precomputed factor:
+// the index arithmetic below would otherwise spend more instructions on runtime divisions
+// than on the data.
+struct SmallDiv {
+  uint32_t m, d;
+  __device__ __forceinline__ explicit SmallDiv(uint32_t d_) : d(d_) {
+    m = d_ > 1 ? 0xFFFFFFFFu / d_ + 1 : 0;  // ceil(2^32 / d)
+  }
+  __device__ __forceinline__ uint32_t operator()(uint32_t n) const {
+    return d == 1 ? n : __umulhi(n, m);
+  }
+};
+
+// Per-tile set-up shared by both layouts: cache block and offset of each of the tile's
+// tokens (block -1 = padding token, skipped), and whether the tile fills 16 consecutive
+// slots that start at a multiple of 16 (true for prefill and chunked writes).
+struct TileSlots {
+  int64_t blk[kTokTile];
+  int off[kTokTile];
+  int full_run;
+};
+
+__device__ __forceinline__ void load_tile_slots(TileSlots& ts, const int64_t* __restrict__ slot_mapping,
+                                                int tok0, int ntok, int block_size) {
+  if (threadIdx.x < 32) {
+    const int t = threadIdx.x;
+    const int64_t slot = t < ntok ? slot_mapping[tok0 + t] : int64_t(-1);
+    if (t < kTokTile) {
+      const int64_t b = slot >= 0 ? slot / block_size : int64_t(-1);
+      ts.blk[t] = b;
+      ts.off[t] = slot >= 0 ? int(slot - b * block_size) : 0;
+    }
+    const int64_t s0 = __shfl_sync(0xffffffffu, slot, 0);
+    const bool in_run = t >= kTokTile || slot == s0 + t;
+    const bool all = __all_sync(0xffffffffu, in_run);
+    if (t == 0)
+      ts.full_run = all && ntok == kTokTile && s0 >= 0 && s0 % kTokTile == 0 &&
+                    block_size % kTokTile == 0;
+  }
+  __syncthreads();
+}
+
+// Plain element-by-element path: scales outside the range ScaledDiv corrects in, x that does
+// not give 16-byte chunks, unaligned tensors.
+template <typename in_t, typename cache_t, int KV>
+__device__ __noinline__ void reshape_tile_generic(const TileSlots& ts, const in_t* key, const in_t* value,
+                                                  cache_t* key_cache, cache_t* value_cache,
+                                                  int64_t key_stride, int64_t value_stride, int tok0,
+                                                  int ntok, int num_heads, int head_size,
+                                                  int block_size, int x, float k_scale, float v_scale) {
+  const int hd = num_heads * head_size;
+  for (int i = threadIdx.x; i < ntok * hd; i += blockDim.x) {
+    const int t = i / hd, r = i % hd;
+    if (ts.blk[t] < 0) continue;
+    const int h = r / head_size, d = r % head_size;
+    const int64_t bh = ts.blk[t] * num_heads + h;
+    const in_t kv = key[int64_t(tok0 + t) * key_stride + r];
+    const in_t vv = value[int64_t(tok0 + t) * value_stride + r];
+    cache_t kq, vq;
+    if constexpr (KV == kKvAuto) {
+      kq = kv;
+      vq = vv;
+    } else {
+      kq = f32_to_fp8<KV == kKvE5M2>(__fdiv_rn(to_f32(kv), k_scale));
+      vq = f32_to_fp8<KV == kKvE5M2>(__fdiv_rn(to_f32(vv), v_scale));
+    }
+    key_cache[((bh * (head_size / x) + d / x) * block_size + ts.off[t]) * x + d % x] = kq;
+    value_cache[(bh * head_size + d) * int64_t(block_size) + ts.off[t]] = vq;
+  }
+}
+
 // grid.x = ceil(num_tokens / kTokTile); block = 256 threads.
 template <typename in_t, typename cache_t, int KV>
 __global__ void __launch_bounds__(256)
@@ -142,192 +209,216 @@ reshape_and_cache_kernel(const in_t* __restrict__ key, const in_t* __restrict__ 
                          int64_t value_stride, int num_tokens, int num_heads, int head_size,
                          int block_size, int x, const float* __restrict__ k_scale_ptr,
                          const float* __restrict__ v_scale_ptr) {
-  __shared__ int64_t s_slot[kTokTile];
+  __shared__ TileSlots ts;
   const int tok0 = blockIdx.x * kTokTile;
   const int ntok = min(kTokTile, num_tokens - tok0);
-  if (threadIdx.x < kTokTile)
-    s_slot[threadIdx.x] = threadIdx.x < ntok ? slot_mapping[tok0 + threadIdx.x] : int64_t(-1);
-  __syncthreads();
+  load_tile_slots(ts, slot_mapping, tok0, ntok, block_size);
 
-  const ScaledDiv k_scale((KV == kKvAuto) ? 1.f : *k_scale_ptr);
-  const ScaledDiv v_scale((KV == kKvAuto) ? 1.f : *v_scale_ptr);
+  const float k_scale_f = (KV == kKvAuto) ? 1.f : *k_scale_ptr;
+  const float v_scale_f = (KV == kKvAuto) ? 1.f : *v_scale_ptr;
+  const ScaledDiv k_scale(k_scale_f), v_scale(v_scale_f);
   const int chunks = head_size / x;  // per head
   const int hd = num_heads * head_size;
-  // 16-byte loads from key/value rows are legal when bases and row strides are 16-byte multiples
-  const bool in_vec_ok =
+  // 16-byte loads from key/value rows are legal when bases and row strides are 16-byte
+  // multiples; x elements = 16 bytes of cache in the standard layout
+  const bool vec_ok =
       ((reinterpret_cast<uintptr_t>(key) | reinterpret_cast<uintptr_t>(value) |
-        (size_t(key_stride) * sizeof(in_t)) | (size_t(value_stride) * sizeof(in_t)) |
-        (size_t(head_size) * sizeof(in_t)) | (size_t(x) * sizeof(in_t))) & 15) == 0;
+        reinterpret_cast<uintptr_t>(key_cache) | (size_t(key_stride) * sizeof(in_t)) |
+        (size_t(value_stride) * sizeof(in_t)) | (size_t(head_size) * sizeof(in_t)) |
+        (size_t(x) * sizeof(in_t))) & 15) == 0 &&
+      x * int(sizeof(cache_t)) == 16 && (KV == kKvAuto || (k_scale.fast && v_scale.fast));
+  if (!vec_ok) {
+    reshape_tile_generic<in_t, cache_t, KV>(ts, key, value, key_cache, value_cache, key_stride,
+                                            value_stride, tok0, ntok, num_heads, head_size,
+                                            block_size, x, k_scale_f, v_scale_f);
+    return;
+  }
 
-  // ---- K: work item = (token, head, chunk); chunk fastest for coalesced reads.
-  const int k_items = ntok * num_heads * chunks;
-  for (int it = threadIdx.x; it < k_items; it += blockDim.x) {
-    const int c = it % chunks;
-    const int h = (it / chunks) % num_heads;
-    const int t = it / (chunks * num_heads);
-    const int64_t slot = s_slot[t];
-    if (slot < 0) continue;
-    const int64_t b = slot / block_size;
-    const int off = int(slot % block_size);
-    const in_t* src = key + int64_t(tok0 + t) * key_stride + h * head_size + c * x;
-    cache_t* dst = key_cache + ((b * num_heads + h) * chunks + c) * int64_t(block_size) * x +
-                   int64_t(off) * x;
-    // x elements = 16 bytes of cache in the standard layout; handle any x generically.
-    if (x * int(sizeof(cache_t)) == 16 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-      constexpr int N = 16 / sizeof(cache_t);        // elements per 16-byte store
-      constexpr int L = N * sizeof(in_t) / 16;       // 16-byte loads that feed it
-      __align__(16) in_t in[N];
-      if (in_vec_ok) {
+  // ---- K: work item = (token, head, chunk), chunk fastest for coalesced reads; one 16-byte
+  // store per item, KB items in flight per thread.
+  {
+    constexpr int N = 16 / sizeof(cache_t);   // elements per 16-byte store
+    constexpr int L = N * sizeof(in_t) / 16;  // 16-byte loads that feed it
+    constexpr int KB = 4;
+    const int per_tok = num_heads * chunks;
+    const int k_items = ntok * per_tok;
+    const SmallDiv by_tok(per_tok), by_chunks(chunks);
+    for (int it0 = threadIdx.x; it0 < k_items; it0 += KB * blockDim.x) {
+      __align__(16) in_t in[KB][N];
+      cache_t* dst[KB];
 #pragma unroll
-        for (int i = 0; i < L; ++i)
-          reinterpret_cast<uint4*>(in)[i] = reinterpret_cast<const uint4*>(src)[i];
-      } else {
+      for (int k = 0; k < KB; ++k) {
+        const int it = it0 + k * blockDim.x;
+        dst[k] = nullptr;
+        if (it < k_items) {
+          const int t = int(by_tok(it));
+          const int j = it - t * per_tok;
+          const int h = int(by_chunks(j));
+          const int c = j - h * chunks;
+          const int64_t b = ts.blk[t];
+          if (b >= 0) {
+            const in_t* src = key + int64_t(tok0 + t) * key_stride + j * x;  // j * x = h * head_size + c * x
+            dst[k] = key_cache + (((b * num_heads + h) * chunks + c) * int64_t(block_size) + ts.off[t]) * x;
 #pragma unroll
-        for (int i = 0; i < N; ++i) in[i] = src[i];
+            for (int i = 0; i < L; ++i)
+              reinterpret_cast<uint4*>(in[k])[i] = reinterpret_cast<const uint4*>(src)[i];
+          }
+        }
       }
-      __align__(16) cache_t vals[N];
-      convert_n<in_t, cache_t, KV, N>(in, vals, k_scale);
-      *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(vals);
-    } else {
-      for (int i = 0; i < x; ++i) dst[i] = store_convert<in_t, cache_t, KV>(src[i], k_scale);
+#pragma unroll
+      for (int k = 0; k < KB; ++k) {
+        if (dst[k] != nullptr) {
+          __align__(16) cache_t vals[N];
+          convert_n<in_t, cache_t, KV, N>(in[k], vals, k_scale);
+          *reinterpret_cast<uint4*>(dst[k]) = *reinterpret_cast<const uint4*>(vals);
+        }
+      }
     }
   }
 
-  // ---- V fast path: the whole tile is one run that fills slots [off, off+16) of one block
-  // (prefill / chunked writes).  A thread takes VD consecutive d of one head, reads them
-  // for the 16 tokens with 16-byte loads and writes VD rows of 16 tokens each.
-  constexpr int VD = 16 / sizeof(in_t);
-  bool full_run = ntok == kTokTile && in_vec_ok && head_size % VD == 0 && block_size % kTokTile == 0;
-  if (full_run) {
-    const int64_t s0 = s_slot[0];
-    full_run = s0 >= 0 && (s0 % kTokTile) == 0;
-#pragma unroll
-    for (int i = 1; i < kTokTile; ++i) full_run = full_run && s_slot[i] == s0 + i;
-    full_run = full_run &&
-               ((reinterpret_cast<uintptr_t>(value_cache) | (size_t(block_size) * sizeof(cache_t))) &
-                (kTokTile * sizeof(cache_t) >= 16 ? 15 : (kTokTile * sizeof(cache_t) - 1))) == 0;
-  }
-  if (full_run) {
-    const int64_t s0 = s_slot[0];
-    const int64_t b = s0 / block_size;
-    const int off = int(s0 % block_size);
+  // ---- V is a transpose ([token][d] -> [d][token in block]).
+  constexpr int VD = 8 / sizeof(in_t);  // d per thread: one 8-byte load per token
+  const bool v_rows_ok =
+      ((reinterpret_cast<uintptr_t>(value_cache) | (size_t(block_size) * sizeof(cache_t))) &
+       (kTokTile * sizeof(cache_t) >= 16 ? 15 : (kTokTile * sizeof(cache_t) - 1))) == 0;
+  if (ts.full_run && v_rows_ok && head_size % VD == 0) {
+    // Fast path: the tile fills slots [off, off+16) of one block.  A thread takes VD
+    // consecutive d of one head for the 16 tokens and writes VD rows of 16 tokens each.
+    const int64_t b = ts.blk[0];
+    const int off = ts.off[0];
     const int groups = hd / VD;
     for (int gidx = threadIdx.x; gidx < groups; gidx += blockDim.x) {
       const int row0 = gidx * VD;  // (head, d) flattened; a group never straddles a head
       const in_t* src = value + int64_t(tok0) * value_stride + row0;
+      __align__(8) in_t in[kTokTile][VD];
+#pragma unroll
+      for (int t = 0; t < kTokTile; ++t)
+        *reinterpret_cast<uint2*>(in[t]) = *reinterpret_cast<const uint2*>(src + int64_t(t) * value_stride);
       __align__(16) cache_t vals[VD][kTokTile];
 #pragma unroll
       for (int t = 0; t < kTokTile; t += 2) {
-        __align__(16) in_t in0[VD], in1[VD];
-        *reinterpret_cast<uint4*>(in0) = *reinterpret_cast<const uint4*>(src + int64_t(t) * value_stride);
-        *reinterpret_cast<uint4*>(in1) =
-            *reinterpret_cast<const uint4*>(src + int64_t(t + 1) * value_stride);
 #pragma unroll
         for (int d = 0; d < VD; ++d) {
-          const in_t two[2] = {in0[d], in1[d]};
+          const in_t two[2] = {in[t][d], in[t + 1][d]};
           convert_n<in_t, cache_t, KV, 2>(two, &vals[d][t], v_scale);
         }
       }
       cache_t* dst = value_cache + (b * hd + row0) * int64_t(block_size) + off;
 #pragma unroll
       for (int d = 0; d < VD; ++d) {
-        constexpr int W = kTokTile * sizeof(cache_t) / 16;  // 16-byte stores per row (0 for 1-byte x 8...)
-        if constexpr (W >= 1) {
+        constexpr int W = kTokTile * sizeof(cache_t) / 16;  // 16-byte stores per row
 #pragma unroll
-          for (int w = 0; w < W; ++w)
-            reinterpret_cast<uint4*>(dst + int64_t(d) * block_size)[w] =
-                reinterpret_cast<const uint4*>(vals[d])[w];
-        }
+        for (int w = 0; w < W; ++w)
+          reinterpret_cast<uint4*>(dst + int64_t(d) * block_size)[w] =
+              reinterpret_cast<const uint4*>(vals[d])[w];
       }
     }
     return;
   }
 
-  // ---- V: thread owns one (head, d) row of the tile; writes runs of consecutive slots.
+  // Ragged tile (decode steps): a thread owns one (head, d) row and writes every run of
+  // tokens that landed in consecutive slots of one block with the widest aligned store.
   for (int row = threadIdx.x; row < hd; row += blockDim.x) {
-    const int h = row / head_size;
-    const int d = row % head_size;
     const in_t* src = value + int64_t(tok0) * value_stride + row;
     int i = 0;
     while (i < ntok) {
-      const int64_t slot = s_slot[i];
-      if (slot < 0) { ++i; continue; }
-      const int64_t b = slot / block_size;
-      const int off = int(slot % block_size);
+      const int64_t b = ts.blk[i];
+      if (b < 0) { ++i; continue; }
+      const int off = ts.off[i];
       int len = 1;
-      while (i + len < ntok && off + len < block_size && s_slot[i + len] == slot + len) ++len;
-      cache_t vals[kTokTile];
+      while (i + len < ntok && ts.blk[i + len] == b && ts.off[i + len] == off + len) ++len;
+      __align__(16) cache_t vals[kTokTile];
 #pragma unroll
       for (int k = 0; k < kTokTile; ++k)
         if (k < len)
           vals[k] = store_convert<in_t, cache_t, KV>(src[int64_t(i + k) * value_stride], v_scale);
-      cache_t* dst = value_cache + ((b * num_heads + h) * head_size + d) * int64_t(block_size) + off;
+      cache_t* dst = value_cache + (b * hd + row) * int64_t(block_size) + off;
       store_run<cache_t, kTokTile>(dst, vals, len);
       i += len;
     }
   }
 }
 
-// One CTA per token; 16-byte vector copies when everything is aligned.
+// Flash layout ([block][slot][head][d], NHD or HND by strides): row copies.  Same tiling as
+// above (16 tokens per CTA, KB 16-byte loads in flight per thread), K pass then V pass so
+// that each pass sets its divider up once.
 template <typename in_t, typename cache_t, int KV>
 __global__ void __launch_bounds__(256)
 reshape_and_cache_flash_kernel(const in_t* __restrict__ key, const in_t* __restrict__ value,
                                cache_t* __restrict__ key_cache, cache_t* __restrict__ value_cache,
                                const int64_t* __restrict__ slot_mapping, int64_t block_stride,
                                int64_t page_stride, int64_t head_stride, int64_t key_stride,
-                               int64_t value_stride, int num_heads, int head_size, int block_size,
-                               int vec_ok, const float* __restrict__ k_scale_ptr,
+                               int64_t value_stride, int num_tokens, int num_heads, int head_size,
+                               int block_size, int vec_ok, const float* __restrict__ k_scale_ptr,
                                const float* __restrict__ v_scale_ptr) {
-  const int64_t token = blockIdx.x;
-  const int64_t slot = slot_mapping[token];
-  if (slot < 0) return;
-  const int64_t b = slot / block_size;
-  const int64_t off = slot % block_size;
-  const float k_scale = (KV == kKvAuto) ? 1.f : *k_scale_ptr;
-  const float v_scale = (KV == kKvAuto) ? 1.f : *v_scale_ptr;
-  const in_t* ksrc = key + token * key_stride;
-  const in_t* vsrc = value + token * value_stride;
-  cache_t* kdst = key_cache + b * block_stride + off * page_stride;
-  cache_t* vdst = value_cache + b * block_stride + off * page_stride;
-
+  __shared__ TileSlots ts;
+  const int tok0 = blockIdx.x * kTokTile;
+  const int ntok = min(kTokTile, num_tokens - tok0);
+  load_tile_slots(ts, slot_mapping, tok0, ntok, block_size);
+  const float k_scale_f = (KV == kKvAuto) ? 1.f : *k_scale_ptr;
+  const float v_scale_f = (KV == kKvAuto) ? 1.f : *v_scale_ptr;
   constexpr int VEC = 16 / sizeof(in_t);  // elements per 16-byte read
-  if (vec_ok) {
-    const int vec_per_head = head_size / VEC;
-    const int items = num_heads * vec_per_head;
-    // a thread's items are K first, then V: the divider is set up once per tensor it touches
-    ScaledDiv scale(k_scale);
-    bool scale_is_v = false;
-    for (int it = threadIdx.x; it < 2 * items; it += blockDim.x) {
-      const bool is_v = it >= items;
-      if (is_v && !scale_is_v) {
-        scale = ScaledDiv(v_scale);
-        scale_is_v = true;
+  constexpr int KB = 4;
+
+#pragma unroll 1
+  for (int pass = 0; pass < 2; ++pass) {
+    const in_t* src_base = pass ? value : key;
+    cache_t* dst_base = pass ? value_cache : key_cache;
+    const int64_t src_stride = pass ? value_stride : key_stride;
+    const float scale_f = pass ? v_scale_f : k_scale_f;
+    const ScaledDiv scale(scale_f);
+    if (vec_ok && (KV == kKvAuto || scale.fast)) {
+      const int vec_per_head = head_size / VEC;
+      const int per_tok = num_heads * vec_per_head;
+      const int items = ntok * per_tok;
+      const SmallDiv by_tok(per_tok), by_head(vec_per_head);
+      for (int it0 = threadIdx.x; it0 < items; it0 += KB * blockDim.x) {
+        __align__(16) in_t in[KB][VEC];
+        cache_t* dst[KB];
+#pragma unroll
+        for (int k = 0; k < KB; ++k) {
+          const int it = it0 + k * blockDim.x;
+          dst[k] = nullptr;
+          if (it < items) {
+            const int t = int(by_tok(it));
+            const int j = it - t * per_tok;
+            const int h = int(by_head(j));
+            const int e = (j - h * vec_per_head) * VEC;
+            const int64_t b = ts.blk[t];
+            if (b >= 0) {
+              dst[k] = dst_base + b * block_stride + ts.off[t] * page_stride + h * head_stride + e;
+              *reinterpret_cast<uint4*>(in[k]) = *reinterpret_cast<const uint4*>(
+                  src_base + int64_t(tok0 + t) * src_stride + h * head_size + e);
+            }
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < KB; ++k) {
+          if (dst[k] != nullptr) {
+            __align__(16) cache_t outv[VEC];
+            convert_n<in_t, cache_t, KV, VEC>(in[k], outv, scale);
+            if constexpr (sizeof(cache_t) * VEC == 16) {
+              *reinterpret_cast<uint4*>(dst[k]) = *reinterpret_cast<const uint4*>(outv);
+            } else if constexpr (sizeof(cache_t) * VEC == 8) {
+              *reinterpret_cast<uint2*>(dst[k]) = *reinterpret_cast<const uint2*>(outv);
+            } else {
+              *reinterpret_cast<uint32_t*>(dst[k]) = *reinterpret_cast<const uint32_t*>(outv);
+            }
+          }
+        }
       }
-      const int j = is_v ? it - items : it;
-      const int h = j / vec_per_head;
-      const int e = (j % vec_per_head) * VEC;
-      const in_t* s = (is_v ? vsrc : ksrc) + h * head_size + e;
-      cache_t* d = (is_v ? vdst : kdst) + h * head_stride + e;
-      __align__(16) in_t in[VEC];
-      *reinterpret_cast<uint4*>(in) = *reinterpret_cast<const uint4*>(s);
-      __align__(16) cache_t outv[VEC];
-      convert_n<in_t, cache_t, KV, VEC>(in, outv, scale);
-      if constexpr (sizeof(cache_t) * VEC == 16) {
-        *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(outv);
-      } else if constexpr (sizeof(cache_t) * VEC == 8) {
-        *reinterpret_cast<uint2*>(d) = *reinterpret_cast<const uint2*>(outv);
-      } else {
-        *reinterpret_cast<uint32_t*>(d) = *reinterpret_cast<const uint32_t*>(outv);
+    } else {
+      const int hd = num_heads * head_size;
+      for (int i = threadIdx.x; i < ntok * hd; i += blockDim.x) {
+        const int t = i / hd, r = i % hd;
+        if (ts.blk[t] < 0) continue;
+        const int h = r / head_size, e = r % head_size;
+        const in_t v = src_base[int64_t(tok0 + t) * src_stride + r];
+        cache_t q;
+        if constexpr (KV == kKvAuto) q = v;
+        else q = f32_to_fp8<KV == kKvE5M2>(__fdiv_rn(to_f32(v), scale_f));
+        dst_base[ts.blk[t] * block_stride + ts.off[t] * page_stride + h * head_stride + e] = q;
       }
-    }
-  } else {
-    const int items = num_heads * head_size;
-    const ScaledDiv kdiv(k_scale), vdiv(v_scale);
-    for (int it = threadIdx.x; it < items; it += blockDim.x) {
-      const int h = it / head_size;
-      const int e = it % head_size;
-      kdst[h * head_stride + e] = store_convert<in_t, cache_t, KV>(ksrc[it], kdiv);
-      vdst[h * head_stride + e] = store_convert<in_t, cache_t, KV>(vsrc[it], vdiv);
     }
   }
 }
@@ -370,11 +461,12 @@ static int launch_reshape(const b200pa_cache_args& a, cudaStream_t stream, bool 
         a.value_stride % VEC == 0 && al(a.key_cache, out_bytes) && al(a.value_cache, out_bytes) &&
         a.block_stride % VEC == 0 && a.page_stride % VEC == 0 && a.head_stride % VEC == 0;
     const int threads = 256;
-    reshape_and_cache_flash_kernel<in_t, cache_t, KV><<<a.num_tokens, threads, 0, stream>>>(
+    dim3 grid((a.num_tokens + kTokTile - 1) / kTokTile);
+    reshape_and_cache_flash_kernel<in_t, cache_t, KV><<<grid, threads, 0, stream>>>(
         static_cast<const in_t*>(a.key), static_cast<const in_t*>(a.value),
         static_cast<cache_t*>(a.key_cache), static_cast<cache_t*>(a.value_cache), a.slot_mapping,
-        a.block_stride, a.page_stride, a.head_stride, a.key_stride, a.value_stride, a.num_heads,
-        a.head_size, a.block_size, vec_ok ? 1 : 0, a.k_scale, a.v_scale);
+        a.block_stride, a.page_stride, a.head_stride, a.key_stride, a.value_stride, a.num_tokens,
+        a.num_heads, a.head_size, a.block_size, vec_ok ? 1 : 0, a.k_scale, a.v_scale);
   }
   count_launch();
   B200PA_CHECK_CUDA(cudaGetLastError());
