@@ -409,15 +409,16 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
       // items start on an even page and a window holds 32: both ids are in this window
 #pragma unroll
       for (int i = 0; i < PP; ++i) prod_blk[i] = __shfl_sync(0xffffffffu, pi_bt, (prod_pg + i) & 31);
-      prod_n = min(PP, pi_npages - prod_pg);
+      if constexpr (PP > 1) prod_n = min(PP, pi_npages - prod_pg);
     }
     if (lane == 0) {
       const uint32_t bar = my_bar0 + prod_slot * 8;
       const uint32_t dst = my_slot0 + prod_slot * slot_bytes;
-      mbar_expect_tx(bar, (split_kv ? 1u : 2u) * uint32_t(prod_n) * page_bytes);
+      const int nblk = PP > 1 ? prod_n : 1;  // blocks in this step
+      mbar_expect_tx(bar, (split_kv ? 1u : 2u) * uint32_t(nblk) * page_bytes);
 #pragma unroll
       for (int i = 0; i < PP; ++i) {
-        if (i < prod_n) {
+        if (i < nblk) {
           const int64_t off = int64_t(prod_blk[i]) * blk_stride_bytes + pi_kvoff;
           if constexpr (split_kv) {
             bulk_g2s(dst + i * page_bytes, (prod_half ? vc_base : kc_base) + off, page_bytes, bar,
@@ -674,14 +675,13 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
         const int rem = cur.tok_end - page_tok0;  // valid tokens of this step, 1 .. ST-1
         const int pl = (rem - 1) / B;             // block of the step that holds the last one
         const int r = rem - pl * B;               // valid tokens in that block
-        const int w = B - r;
         unsigned char* vpage = slots + (size_t(warp) * NSLOT + cons_slot) * slot_bytes +
                                (split_kv ? 0u : step_bytes) + pl * page_bytes;
-        for (int idx = lane; idx < D * w; idx += 32) {
-          const int d = idx / w;
-          const int tk = r + idx % w;
-          if constexpr (ES == 1) vpage[d * B + tk] = 0;
-          else reinterpret_cast<uint16_t*>(vpage)[d * B + tk] = 0;
+        for (int d = lane; d < D; d += 32) {
+          for (int tk = r; tk < B; ++tk) {
+            if constexpr (ES == 1) vpage[d * B + tk] = 0;
+            else reinterpret_cast<uint16_t*>(vpage)[d * B + tk] = 0;
+          }
         }
         __syncwarp();
       }
