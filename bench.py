@@ -45,7 +45,7 @@ FALLBACK_HBM_GBS = 6650.0
 # algorithmic bytes of that launch, from ncu captures of small cases of the same kernels (64
 # sequences of the bf16 workload, 16 sequences of the fp8 workload; their summaries are kept with
 # the other profiler summaries of this repository).  Traffic grows in proportion to tokens.
-NCU_TRAFFIC_RATIO = {"cfg2": 1.019, "cfg4": 1.019, "cfg3": 1.027, "cfg5": 1.027}
+NCU_TRAFFIC_RATIO = {"cfg2": 1.010, "cfg4": 1.010, "cfg3": 1.014, "cfg5": 1.014}
 
 
 def measured_peak():
