@@ -9,7 +9,7 @@ constexpr int kPartitionTokens = 512;  // split-KV partition, same as the refere
 constexpr float kLog2e = 1.4426950408889634f;
 
 // Status codes written to the device status word.
-enum : int { kStatusOk = 0, kStatusMbarTimeout = 1 };
+enum : int { kStatusOk = 0, kStatusMbarTimeout = 1, kStatusNoRing = 2 };
 
 struct DecodeParams {
   void* out;

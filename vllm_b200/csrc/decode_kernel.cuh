@@ -234,7 +234,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
   constexpr int ST = 16 * NT;  // tokens per step
   constexpr uint32_t page_bytes = uint32_t(D) * B * (KV != kCache16 ? 1 : 2);
   constexpr uint32_t step_bytes = PP * page_bytes;  // K (or V) bytes of one step
-  const int NSLOT = p.nstages;  // ring slots of this warp
+  const int slots_per_warp = p.nstages;  // ring slots the launch provides per warp
   // Steps of 4 KiB and more get one slot and one barrier each for K and V (finer prefetch
   // granularity: the K slot is refilled while the softmax runs); smaller ones share one slot
   // and one barrier (half the barrier traffic).  The host uses the same rule.
@@ -246,11 +246,9 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
   int* cum = reinterpret_cast<int*>(smem_raw);
   const int table_ints = p.use_table ? ((p.num_seqs + 1 + 3) & ~3) : 0;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + size_t(table_ints) * 4);
-  const uint32_t bars_bytes = (uint32_t(nwarps) * NSLOT * 8 + 127u) & ~127u;
+  const uint32_t bars_bytes = (uint32_t(nwarps) * slots_per_warp * 8 + 127u) & ~127u;
   unsigned char* slots = smem_raw + size_t(table_ints) * 4 + bars_bytes;
   // the dynamic buffer is 128-byte aligned and table_ints*4 is a multiple of 16
-  const uint32_t my_slot0 = smem_u32(slots) + uint32_t(warp) * NSLOT * slot_bytes;
-  const uint32_t my_bar0 = smem_u32(bars) + uint32_t(warp) * NSLOT * 8;
 
   // ---- set-up: prefix table of partitions per sequence (exclusive scan)
   if (p.use_table) {
@@ -282,15 +280,32 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
     }
     if (threadIdx.x == blockDim.x - 1) cum[S] = run;
   }
-  if (lane == 0) {
-    for (int s = 0; s < NSLOT; ++s) mbar_init(my_bar0 + s * 8, 1);
-    fence_barrier_init();
-  }
   __syncthreads();
 
   const int hsubs = p.num_kv_heads * p.head_groups;
   const int total_parts = p.use_table ? cum[p.num_seqs] : p.num_seqs;
   const unsigned total_items = unsigned(total_parts) * unsigned(hsubs);
+
+  // Ring of this warp.  The host sizes warps and slots from max_seq_len, the only length it
+  // knows; when the batch turns out to have fewer items than the grid has warps, the warps
+  // without an item (the highest-numbered ones of each CTA, see the item numbering below)
+  // leave their slots and barriers to the others: fewer busy warps, each with more pages in
+  // flight, which is what a launch bound by the latency of one item needs.
+  int NSLOT = slots_per_warp;
+  if (total_items < gridDim.x * unsigned(nwarps)) {
+    const int busy = max(1, int((total_items + gridDim.x - 1) / gridDim.x));  // per CTA, at most
+    NSLOT = min(8, nwarps * slots_per_warp / busy);
+  }
+  const uint32_t my_slot0 = smem_u32(slots) + uint32_t(warp) * NSLOT * slot_bytes;
+  const uint32_t my_bar0 = smem_u32(bars) + uint32_t(warp) * NSLOT * 8;
+  unsigned char* my_slots = slots + size_t(warp) * NSLOT * slot_bytes;
+  const bool has_ring = (warp + 1) * NSLOT <= nwarps * slots_per_warp;
+  if (lane == 0 && has_ring) {
+    // the barriers are private to the warp: no CTA-wide synchronisation after their set-up
+    for (int s = 0; s < NSLOT; ++s) mbar_init(my_bar0 + s * 8, 1);
+    fence_barrier_init();
+  }
+  __syncwarp();
   const uint64_t policy = policy_evict_first();
   const char* kc_base = static_cast<const char*>(p.kc);
   const char* vc_base = static_cast<const char*>(p.vc);
@@ -368,6 +383,11 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
   }
   WorkItem nxt = decode(raw1);
   unsigned nn_raw = raw2;
+  if (!has_ring && cur.valid) {
+    // cannot happen with the item numbering above; never touch slots that are not this warp's
+    if (lane == 0) atomicExch(p.status, kStatusNoRing);
+    cur.valid = false;
+  }
 
   // ---- producer state.  The ring is filled in the order K(page 0), V(page 0), K(page 1), ...
   int prod_sel = 0;   // 0: producing pages of `cur`, 1: of `nxt`
@@ -675,7 +695,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
         const int rem = cur.tok_end - page_tok0;  // valid tokens of this step, 1 .. ST-1
         const int pl = (rem - 1) / B;             // block of the step that holds the last one
         const int r = rem - pl * B;               // valid tokens in that block
-        unsigned char* vpage = slots + (size_t(warp) * NSLOT + cons_slot) * slot_bytes +
+        unsigned char* vpage = my_slots + size_t(cons_slot) * slot_bytes +
                                (split_kv ? 0u : step_bytes) + pl * page_bytes;
         for (int d = lane; d < D; d += 32) {
           for (int tk = r; tk < B; ++tk) {
