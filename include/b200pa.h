@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define B200PA_VERSION 1
+#define B200PA_VERSION 2
 
 /* Error codes (negative). */
 #define B200PA_OK 0
@@ -127,6 +127,15 @@ typedef struct b200pa_attn_args {
   int32_t blocksparse_vert_stride;
   int32_t blocksparse_block_size;
   int32_t blocksparse_head_sliding_step;
+
+  /* Optional extra output, NULL in the reference's calls (its ops have no such
+   * argument): out_lse[head * num_seqs + seq] = natural log of the sum over the
+   * sequence's tokens of exp(scaled logit + ALiBi bias), float32, -inf for an empty
+   * sequence.  Layout [num_heads, num_seqs] as merge_attn_states takes it
+   * (csrc/attention/merge_attn_states.cu:14-30), so that attention over disjoint
+   * token ranges of a sequence - on one GPU or one range per rank - can be combined
+   * with b200pa_merge_attn_states. */
+  float* out_lse;
 } b200pa_attn_args;
 
 /* Replaces paged_attention_v1 (csrc/attention/paged_attention_v1.cu:160-182).  No scratch

@@ -179,7 +179,7 @@ def blocksparse_mask(seq_len, block_size, num_heads, num_kv_heads, tp_rank, loca
 
 def paged_attention(query, key_cache, value_cache, num_kv_heads, scale, block_tables, seq_lens,
                     alibi_slopes=None, kv_cache_dtype="auto", k_scale=1.0, v_scale=1.0,
-                    mode="ref", partition_size=None, seqs=None, blocksparse=None):
+                    mode="ref", partition_size=None, seqs=None, blocksparse=None, return_lse=False):
     """Decode attention over a paged KV cache; returns ``out`` [S, Hq, D].
 
     mode="ref": reference rounding points, result in the query dtype.
@@ -188,11 +188,16 @@ def paged_attention(query, key_cache, value_cache, num_kv_heads, scale, block_ta
     seqs: optional iterable of sequence indices to compute (others are left zero).
     blocksparse: None or (tp_rank, local_blocks, vert_stride, block_size, head_sliding_step);
         only with mode="f64" (masked tokens get zero weight).
+    return_lse: with mode="f64" also return lse [Hq, S] float64, the natural log of the sum of
+        exp(scaled logit + bias) over each sequence's tokens (-inf for an empty sequence): the
+        quantity merge_attn_states combines partial attention results with.
     """
     S, Hq, D = query.shape
     G = Hq // num_kv_heads
     T = query.dtype
     out = torch.zeros((S, Hq, D), dtype=torch.float64 if mode == "f64" else T)
+    lse = torch.full((Hq, S), -math.inf, dtype=torch.float64)
+    assert not return_lse or mode == "f64"
     lens = seq_lens.tolist()
     for s in (range(S) if seqs is None else seqs):
         L = int(lens[s])
@@ -216,6 +221,7 @@ def paged_attention(query, key_cache, value_cache, num_kv_heads, scale, block_ta
                 logits = logits.masked_fill(~keep, -math.inf)
             p = torch.softmax(logits, dim=1)
             out[s] = torch.einsum("hn,nhd->hd", p, v.double())
+            lse[:, s] = torch.logsumexp(logits, dim=1)
             continue
         if partition_size is None:
             o, _, _ = _attend_ref(q, k, v, scale, alibi_slopes, L, 0, T)
@@ -241,7 +247,7 @@ def paged_attention(query, key_cache, value_cache, num_kv_heads, scale, block_ta
         r = ls * torch.exp(ms - M.view(1, -1))
         inv = 1.0 / (r.sum(dim=0) + 1e-6)
         out[s] = (tmp * r.unsqueeze(-1) * inv.view(1, -1, 1)).sum(dim=0).to(T)
-    return out
+    return (out, lse) if return_lse else out
 
 
 def attn_bytes(seq_lens, num_heads, num_kv_heads, head_size, block_size, q_bytes, cache_bytes):

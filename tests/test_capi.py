@@ -26,13 +26,14 @@ def test_header_symbols_are_exported():
 
 
 def test_struct_sizes_match_header_layout():
-    # 12 pointers + 3 int64 + 8 int32 + float + 2 int32 + 5 int32 = 96+24+64 = 184
-    assert C.sizeof(capi.AttnArgs) == 12 * 8 + 3 * 8 + 16 * 4
+    # 12 pointers + 3 int64 + 8 int32 + float + 2 int32 + 5 int32 + out_lse = 96+24+64+8 = 192
+    assert C.sizeof(capi.AttnArgs) == 12 * 8 + 3 * 8 + 16 * 4 + 8
+    assert capi.AttnArgs.out_lse.offset == 184
     assert C.sizeof(capi.CacheArgs) == 7 * 8 + 5 * 8 + 7 * 4 + 4  # tail padding to 8
 
 
 def test_version_and_kv_dtype_strings():
-    assert capi.lib().b200pa_version() == 1
+    assert capi.lib().b200pa_version() == 2
     assert capi.kv_dtype_from_string("auto") == capi.KV_AUTO
     for s in ("fp8", "fp8_e4m3", "fp8_ds_mla"):
         assert capi.kv_dtype_from_string(s) == capi.KV_FP8_E4M3

@@ -1,6 +1,7 @@
 """CUDA-graph capture of the ops (the reference captures them in its decode graphs,
 benchmarks/kernels/benchmark_reshape_and_cache.py:83-88) and the multi-GPU verification path:
-outputs of head- or sequence-sharded ranks, all-gathered over NCCL, equal the unsharded result."""
+outputs of head-, sequence- or token-sharded ranks, all-gathered over NCCL (and, for token
+shards, merged through their log-sum-exps), equal the unsharded result."""
 import os
 import socket
 import sys
@@ -87,6 +88,10 @@ def _rank_main(rank, world, port, q):
                 got = torch.empty_like(want)
                 dist.all_gather_into_tensor(got, out)
             ok.append(bool(torch.equal(got, want)))
+        # tokens of every sequence per rank: partial outputs + log-sum-exps, two all-gathers, merge
+        from vllm_b200 import context_parallel
+        got = context_parallel.decode(Wl.shard_tokens(full, world, rank))
+        ok.append(bool(torch.allclose(got.float(), want.float(), atol=1e-2, rtol=1e-2)))
         q.put((rank, ok))
     finally:
         dist.destroy_process_group()
@@ -108,4 +113,4 @@ def test_sharded_ranks_reassemble_over_nccl():
         p.join(timeout=60)
         assert p.exitcode == 0
     for rank, ok in res:
-        assert ok == [True, True], f"rank {rank}: kv-head / sequence sharding mismatch {ok}"
+        assert ok == [True, True, True], f"rank {rank}: kv-head / sequence / token sharding mismatch {ok}"

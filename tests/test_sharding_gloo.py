@@ -1,6 +1,7 @@
-"""Multi-rank host logic on CPU (gloo, world_size 2): the two partitionings the
-decode path supports — KV heads per rank and sequences per rank with local block
-pools — reproduce the unsharded result when the rank outputs are all-gathered.
+"""Multi-rank host logic on CPU (gloo, world_size 2): the partitionings the decode path
+supports — KV heads per rank, sequences per rank with local block pools, and the tokens of
+every sequence per rank (merged through their log-sum-exps) — reproduce the unsharded result
+when the rank outputs are all-gathered.
 The compute on each rank is the CPU oracle (the product itself has no CPU path);
 what is under test is the sharding plan and the gather layout."""
 import os
@@ -57,10 +58,32 @@ def _worker(rank, world, port, q):
         dist.all_gather(parts, out)
         ok_seqs = torch.equal(torch.cat(parts, dim=0), want)
 
+        # (iii) tokens of every sequence per rank: partial outputs and their log-sum-exps are
+        # all-gathered and combined with the merge_attn_states formula
+        from oracle import paged_oracle as O
+        mine = W.shard_tokens(full, world, rank)
+        assert int(mine.seq_lens.sum()) < int(full.seq_lens.sum())
+        o, l = O.paged_attention(mine.query, mine.key_cache, mine.value_cache, mine.num_kv_heads,
+                                 mine.scale, mine.block_tables, mine.seq_lens, None,
+                                 mine.kv_cache_dtype, float(mine.k_scale), float(mine.v_scale),
+                                 mode="f64", return_lse=True)
+        outs = [torch.empty_like(o) for _ in range(world)]
+        lses = [torch.empty_like(l) for _ in range(world)]
+        dist.all_gather(outs, o.contiguous())
+        dist.all_gather(lses, l.contiguous())
+        acc_o, acc_l = outs[0], lses[0]
+        for o2, l2 in zip(outs[1:], lses[1:]):
+            acc_o, acc_l = O.merge_attn_states(acc_o, acc_l, o2, l2)
+        want64 = O.paged_attention(full.query, full.key_cache, full.value_cache, full.num_kv_heads,
+                                   full.scale, full.block_tables, full.seq_lens, None,
+                                   full.kv_cache_dtype, float(full.k_scale), float(full.v_scale),
+                                   mode="f64")
+        ok_tokens = bool(torch.allclose(acc_o.double(), want64, atol=1e-5, rtol=1e-5))
+
         # timing aggregation used by bench.py: max over ranks
         t = torch.tensor([1.0 + rank], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        q.put((rank, ok_heads, ok_seqs, float(t)))
+        q.put((rank, ok_heads, ok_seqs and ok_tokens, float(t)))
     finally:
         dist.destroy_process_group()
 

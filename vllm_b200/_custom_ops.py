@@ -125,6 +125,32 @@ def convert_fp8(
     _cache_ops.convert_fp8(output, input, scale, kv_dtype)
 
 
+def paged_attention_with_lse(
+    out: torch.Tensor,
+    lse: torch.Tensor,
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    num_kv_heads: int,
+    scale: float,
+    block_tables: torch.Tensor,
+    seq_lens: torch.Tensor,
+    block_size: int,
+    max_seq_len: int,
+    alibi_slopes: torch.Tensor | None,
+    kv_cache_dtype: str,
+    k_scale: torch.Tensor,
+    v_scale: torch.Tensor,
+) -> None:
+    """``paged_attention_v1`` that also fills ``lse`` [num_heads, num_seqs] (float32) with the
+    natural log-sum-exp of each sequence's scaled logits, in the layout ``merge_attn_states``
+    takes.  The reference's paged-attention ops have no such output; its decode context
+    parallelism gets the LSE from other backends (vllm/attention/ops/common.py:172-205)."""
+    torch.ops._C_b200.paged_attention_with_lse(
+        out, lse, query, key_cache, value_cache, num_kv_heads, scale, block_tables, seq_lens,
+        block_size, max_seq_len, alibi_slopes, kv_cache_dtype, k_scale, v_scale)
+
+
 def merge_attn_states(
     output: torch.Tensor,
     prefix_output: torch.Tensor,

@@ -48,6 +48,7 @@ class AttnArgs(C.Structure):
         ("tp_rank", C.c_int32), ("blocksparse_local_blocks", C.c_int32),
         ("blocksparse_vert_stride", C.c_int32), ("blocksparse_block_size", C.c_int32),
         ("blocksparse_head_sliding_step", C.c_int32),
+        ("out_lse", C.c_void_p),
     ]
 
 

@@ -7,6 +7,7 @@ namespace b200pa {
 
 constexpr int kPartitionTokens = 512;  // split-KV partition, same as the reference's PARTITION_SIZE
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
 
 // Status codes written to the device status word.
 enum : int { kStatusOk = 0, kStatusMbarTimeout = 1, kStatusNoRing = 2 };
@@ -46,6 +47,7 @@ struct DecodeParams {
   // block-sparse attention of the reference signature (generic kernel only); enabled when
   // bs_vert_stride > 1 (attention_kernels.cuh:204-251)
   int tp_rank;
+  float* lse;  // optional [num_heads, num_seqs] log-sum-exp output (natural log), or nullptr
   int bs_local_blocks;
   int bs_vert_stride;
   int bs_block_size;

@@ -83,7 +83,7 @@ __device__ __forceinline__ int load_bt(const DecodeParams& p, const WorkItem& it
 template <typename QT, int D>
 __device__ __noinline__ void merge_partials(float* exp_sums, const float* max_logits,
                                             const QT* tmp, QT* outp, int64_t row0, int np, int P,
-                                            int nheads, int lane) {
+                                            int nheads, int lane, float* lse, int lse_stride) {
   constexpr bool kOutBf = std::is_same_v<QT, __nv_bfloat16>;
   // Phase 1: per head, turn (max logit, exp sum) of its partitions into normalised weights.
   // Lanes run over partitions, four heads share one memory round trip.
@@ -117,6 +117,8 @@ __device__ __noinline__ void merge_partials(float* exp_sums, const float* max_lo
       const float winv = __fdividef(1.f, sum + 1e-6f);
       if (lane < np) es[lane] = w0 * winv;
       for (int j = lane + 32; j < np; j += 32) es[j] *= winv;
+      // log-sum-exp of the whole sequence (logits are kept in the log2 domain)
+      if (lse != nullptr && lane == 0) lse[int64_t(h0 + k) * lse_stride] = (mx + log2f(sum)) * kLn2;
     }
   }
   __syncwarp();  // weights written by other lanes are read below
@@ -796,6 +798,9 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
           p.max_logits[idx] = m_run[nt][j];
           p.exp_sums[idx] = l;
         }
+        if (direct && p.lse != nullptr && g == 0 && hl < nheads)
+          p.lse[int64_t(hq0 + hl) * p.num_seqs + cur.seq] =
+              l > 0.f ? (m_run[nt][j] + log2f(l)) * kLn2 : -INFINITY;
       }
       const int hl_t = nt * 8 + g;  // head owned after the transpose
 #pragma unroll
@@ -830,7 +835,9 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
         merge_partials<QT, D>(p.exp_sums, p.max_logits, static_cast<const QT*>(p.tmp_out),
                               static_cast<QT*>(p.out) + (int64_t(cur.seq) * p.num_heads + hq0) * D,
                               (int64_t(cur.seq) * p.num_heads + hq0) * p.max_partitions,
-                              cur.nparts, p.max_partitions, nheads, lane);
+                              cur.nparts, p.max_partitions, nheads, lane,
+                              p.lse ? p.lse + int64_t(hq0) * p.num_seqs + cur.seq : nullptr,
+                              p.num_seqs);
       }
     }
 

@@ -24,7 +24,8 @@ __global__ void pa_reduce_kernel(QT* __restrict__ out, const QT* __restrict__ tm
                                  const float* __restrict__ exp_sums,
                                  const float* __restrict__ max_logits,
                                  const int* __restrict__ seq_lens, int num_seqs, int num_heads,
-                                 int head_size, int max_partitions, int part_tokens) {
+                                 int head_size, int max_partitions, int part_tokens,
+                                 float* __restrict__ lse) {
   extern __shared__ float s_w[];  // [warps][max_partitions]
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -51,6 +52,8 @@ __global__ void pa_reduce_kernel(QT* __restrict__ out, const QT* __restrict__ tm
   for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
   __syncwarp();
   const float inv = __fdividef(1.f, sum + 1e-6f);
+  if (lse != nullptr && lane == 0)
+    lse[int64_t(item % num_heads) * num_seqs + seq] = (mx + log2f(sum)) * kLn2;
   const QT* tp = tmp_out + int64_t(item) * max_partitions * head_size;
   QT* op = out + int64_t(item) * head_size;
   for (int d = lane; d < head_size; d += 32) {
@@ -186,6 +189,8 @@ pa_generic_kernel(const DecodeParams p, int head_size, int x) {
   QT* o;
   if (direct) {
     o = static_cast<QT*>(p.out) + (int64_t(seq) * p.num_heads + head) * head_size;
+    if (p.lse != nullptr && lane == 0)
+      p.lse[int64_t(head) * p.num_seqs + seq] = l > 0.f ? (m + log2f(l)) * kLn2 : -INFINITY;
   } else {
     const int64_t idx = (int64_t(seq) * p.num_heads + head) * p.max_partitions + part;
     o = static_cast<QT*>(p.tmp_out) + idx * head_size;
@@ -322,7 +327,7 @@ static int launch_reduce(const DecodeParams& p, int head_size, cudaStream_t s) {
   const size_t smem = size_t(warps) * p.max_partitions * sizeof(float);
   pa_reduce_kernel<QT><<<grid, warps * 32, smem, s>>>(
       static_cast<QT*>(p.out), static_cast<const QT*>(p.tmp_out), p.exp_sums, p.max_logits,
-      p.seq_lens, p.num_seqs, p.num_heads, head_size, p.max_partitions, p.part_tokens);
+      p.seq_lens, p.num_seqs, p.num_heads, head_size, p.max_partitions, p.part_tokens, p.lse);
   count_launch();
   B200PA_CHECK_CUDA(cudaGetLastError());
   return B200PA_OK;
@@ -419,6 +424,7 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
   p.group = a->num_heads / a->num_kv_heads;
   p.scale = a->scale;
   p.tp_rank = a->tp_rank;
+  p.lse = a->out_lse;
   p.bs_local_blocks = a->blocksparse_local_blocks;
   p.bs_vert_stride = a->blocksparse_vert_stride;
   p.bs_block_size = a->blocksparse_block_size;

@@ -134,6 +134,28 @@ void paged_attention_v1(torch::Tensor& out, torch::Tensor& query, torch::Tensor&
   check_rc(b200pa_paged_attention_v1(&a, at::cuda::getCurrentCUDAStream().stream()));
 }
 
+// paged_attention_v1 that also returns the log-sum-exp of every (head, sequence), the
+// quantity merge_attn_states needs to combine attention over disjoint token ranges.  Not
+// an op of the reference: registered under the _C_b200 namespace only.
+void paged_attention_with_lse(torch::Tensor& out, torch::Tensor& lse, torch::Tensor& query,
+                              torch::Tensor& key_cache, torch::Tensor& value_cache,
+                              int64_t num_kv_heads, double scale, torch::Tensor& block_tables,
+                              torch::Tensor& seq_lens, int64_t block_size, int64_t max_seq_len,
+                              const std::optional<torch::Tensor>& alibi_slopes,
+                              const std::string& kv_cache_dtype, torch::Tensor& k_scale,
+                              torch::Tensor& v_scale) {
+  b200pa_attn_args a;
+  fill_attn(a, out, query, key_cache, value_cache, num_kv_heads, scale, block_tables, seq_lens,
+            block_size, max_seq_len, alibi_slopes, kv_cache_dtype, k_scale, v_scale, 0, 0, 0, 64, 0);
+  check_cuda(lse, "lse");
+  TORCH_CHECK(lse.scalar_type() == at::ScalarType::Float && lse.is_contiguous() && lse.dim() == 2 &&
+                  lse.size(0) == query.size(1) && lse.size(1) == query.size(0),
+              "lse must be a contiguous float32 tensor [num_heads, num_seqs]");
+  a.out_lse = lse.data_ptr<float>();
+  const at::cuda::OptionalCUDAGuard device_guard(device_of(query));
+  check_rc(b200pa_paged_attention_v1(&a, at::cuda::getCurrentCUDAStream().stream()));
+}
+
 void paged_attention_v2(torch::Tensor& out, torch::Tensor& exp_sums, torch::Tensor& max_logits,
                         torch::Tensor& tmp_out, torch::Tensor& query, torch::Tensor& key_cache,
                         torch::Tensor& value_cache, int64_t num_kv_heads, double scale,
@@ -428,6 +450,12 @@ TORCH_LIBRARY(_C_b200, ops) {
   ops.impl("paged_attention_v2", torch::kCUDA, &paged_attention_v2);
   ops.def(kMergeSchema);
   ops.impl("merge_attn_states", torch::kCUDA, &merge_attn_states);
+  ops.def(
+      "paged_attention_with_lse(Tensor! out, Tensor! lse, Tensor query, Tensor key_cache,"
+      " Tensor value_cache, int num_kv_heads, float scale, Tensor block_tables, Tensor seq_lens,"
+      " int block_size, int max_seq_len, Tensor? alibi_slopes, str kv_cache_dtype,"
+      " Tensor k_scale, Tensor v_scale) -> ()");
+  ops.impl("paged_attention_with_lse", torch::kCUDA, &paged_attention_with_lse);
 }
 
 TORCH_LIBRARY(_C_b200_cache_ops, cache_ops) {

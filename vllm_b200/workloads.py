@@ -316,3 +316,46 @@ def shard_sequences(w: Workload, world_size: int, rank: int) -> Workload:
         key_cache=w.key_cache[idx].contiguous(), value_cache=w.value_cache[idx].contiguous(),
         block_tables=torch.from_numpy(local).to(w.block_tables.device),
         seq_lens=w.seq_lens[ss].contiguous())
+
+
+def token_ranges(seq_lens, block_size: int, world_size: int, rank: int):
+    """Block range [b0, b1) and token count of rank `rank` for every sequence when the tokens
+    of each sequence are partitioned across ranks at block boundaries (contiguous ranges of
+    ceil-divided blocks; the last non-empty range carries the ragged tail).  Pure host logic."""
+    lens = np.asarray(seq_lens, dtype=np.int64)
+    nblk = (lens + block_size - 1) // block_size
+    per = (nblk + world_size - 1) // world_size
+    b0 = np.minimum(nblk, rank * per)
+    b1 = np.minimum(nblk, (rank + 1) * per)
+    toks = np.clip(np.minimum(lens, b1 * block_size) - b0 * block_size, 0, None)
+    return b0, b1, toks
+
+
+def shard_tokens(w: Workload, world_size: int, rank: int) -> Workload:
+    """Rank `rank`'s share of `w` when the KV tokens of every sequence are partitioned across
+    ranks (decode context parallelism): a private block pool with only this rank's blocks, block
+    tables and seq_lens rewritten for the local token range; the query is replicated.  Attention
+    over the shards is combined with `context_parallel.merge_partials` (needs the LSE output).
+    ALiBi is not supported here (its bias depends on the global position)."""
+    assert w.alibi_slopes is None
+    lens = w.seq_lens.cpu().numpy().astype(np.int64)
+    b0, b1, toks = token_ranges(lens, w.block_size, world_size, rank)
+    bt = w.block_tables.cpu().numpy()
+    S = w.num_seqs
+    used = np.concatenate([bt[s, b0[s]:b1[s]] for s in range(S)]) if S else np.zeros(0, np.int64)
+    uniq, inv = np.unique(used, return_inverse=True)
+    if uniq.size == 0:
+        uniq = np.zeros(1, dtype=np.int64)
+    local = np.zeros((S, max(1, int((b1 - b0).max()) if S else 1)), dtype=bt.dtype)
+    off = 0
+    for s in range(S):
+        n = int(b1[s] - b0[s])
+        local[s, :n] = inv[off:off + n]
+        off += n
+    idx = torch.from_numpy(uniq.astype(np.int64)).to(w.key_cache.device)
+    return dataclasses.replace(
+        w, name=f"{w.name}/tokens{rank}of{world_size}",
+        key_cache=w.key_cache[idx].contiguous(), value_cache=w.value_cache[idx].contiguous(),
+        block_tables=torch.from_numpy(local).to(w.block_tables.device),
+        seq_lens=torch.from_numpy(toks.astype(np.int32)).to(w.seq_lens.device),
+        max_seq_len=max(1, int(toks.max()) if S else 1))
