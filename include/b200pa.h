@@ -287,6 +287,15 @@ int b200pa_version(void);
  */
 int b200pa_device_status(int32_t* status);
 
+/*
+ * Puts the library's device-side bookkeeping of the current device back to its initial state:
+ * the work-distribution words and split-KV arrival counters of the decode kernel (which every
+ * healthy launch leaves zeroed by itself) and the status word.  Only needed after a launch
+ * reported a non-zero status, whose warps may have left early; enqueued on `stream`, which
+ * must be ordered after every attention call still in flight.  No counterpart in the reference.
+ */
+int b200pa_reset_device_state(void* stream);
+
 /* Number of kernel launches issued by this library on the calling thread since
  * the last call with reset != 0 (host-side counter, for benchmark bookkeeping). */
 int64_t b200pa_launch_count(int reset);

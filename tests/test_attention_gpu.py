@@ -368,3 +368,16 @@ def test_items_per_warp_regimes(num_seqs):
     # every sequence, against plain fp32 attention
     got = W.run_attention(w, version="v2").float()
     torch.testing.assert_close(got, _torch_fp32_reference(w), atol=1e-2, rtol=1e-2)
+
+
+def test_reset_device_state_keeps_the_library_usable():
+    """The reset entry point zeroes words that healthy launches leave zeroed anyway, so results
+    before and after it are identical bits (split and unsplit, tickets and strided items)."""
+    w = W.small(DEV, seed=17, num_seqs=9, num_heads=8, num_kv_heads=2, max_len=3000, num_blocks=1800)
+    before = [W.run_attention(w, version=v).clone() for v in ("v1", "v2")]
+    capi.reset_device_state(torch.cuda.current_stream().cuda_stream)
+    after = [W.run_attention(w, version=v).clone() for v in ("v1", "v2")]
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    for a, b in zip(before, after):
+        assert torch.equal(a, b)

@@ -115,3 +115,28 @@ def test_config_plans_match_the_stated_shapes():
         used |= set(w.block_tables[s, :n].tolist())
     assert len(used) == tot                                  # globally unique blocks
     assert w.key_cache.shape[0] == int(np.ceil(1.25 * tot))
+
+
+def test_token_ranges_cover_every_token_once_at_block_boundaries():
+    """Token sharding plan (decode context parallelism): the ranks' ranges of a sequence are
+    block-aligned, contiguous, disjoint and together cover it; the ragged tail goes to one rank."""
+    import numpy as np
+    from vllm_b200 import workloads as W
+
+    lens = np.array([0, 1, 15, 16, 17, 700, 4096, 4097, 33])
+    for block_size in (16, 32):
+        for world in (1, 2, 3, 8):
+            total = np.zeros_like(lens)
+            prev_end = np.zeros_like(lens)
+            for rank in range(world):
+                b0, b1, toks = W.token_ranges(lens, block_size, world, rank)
+                assert np.all(b0 == prev_end) and np.all(b1 >= b0)
+                full = (b1 - b0) * block_size
+                assert np.all(toks <= full) and np.all(toks >= 0)
+                # only the range that ends the sequence may be ragged
+                ragged = toks < full
+                assert np.all(b1[ragged] * block_size >= lens[ragged])
+                total += toks
+                prev_end = b1
+            assert np.array_equal(total, lens)
+            assert np.array_equal(prev_end, (lens + block_size - 1) // block_size)

@@ -133,5 +133,11 @@ def device_status() -> int:
     return v.value
 
 
+def reset_device_state(stream: int = 0) -> None:
+    """Zeroes the decode kernel's device-side bookkeeping (see b200pa.h); only needed after a
+    launch reported a non-zero device status."""
+    check(lib().b200pa_reset_device_state(C.c_void_p(stream)))
+
+
 def launch_count(reset: bool = False) -> int:
     return int(lib().b200pa_launch_count(1 if reset else 0))

@@ -677,3 +677,23 @@ extern "C" int b200pa_paged_attention_v2_noalloc(const b200pa_attn_args* args, v
   a.max_num_partitions = static_cast<int32_t>(parts);
   return attention_entry(&a, stream, true);
 }
+
+extern "C" int b200pa_reset_device_state(void* stream) {
+  using namespace b200pa;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  unsigned* sched = nullptr;
+  unsigned* arrive = nullptr;
+  int* status = device_status_ptr();
+  if (!launch_slots(&sched, &arrive) || status == nullptr) {
+    set_error("could not resolve device-side scheduler/status words");
+    return B200PA_ECUDA;
+  }
+  void* sbase = nullptr;
+  void* abase = nullptr;
+  B200PA_CHECK_CUDA(cudaGetSymbolAddress(&sbase, g_sched_words));
+  B200PA_CHECK_CUDA(cudaGetSymbolAddress(&abase, g_arrive));
+  B200PA_CHECK_CUDA(cudaMemsetAsync(sbase, 0, sizeof(g_sched_words), s));
+  B200PA_CHECK_CUDA(cudaMemsetAsync(abase, 0, sizeof(g_arrive), s));
+  B200PA_CHECK_CUDA(cudaMemsetAsync(status, 0, sizeof(int), s));
+  return B200PA_OK;
+}
