@@ -381,3 +381,54 @@ def test_reset_device_state_keeps_the_library_usable():
     assert capi.device_status() == 0
     for a, b in zip(before, after):
         assert torch.equal(a, b)
+
+
+def _torch_reference_any(w):
+    """fp32 attention over the gathered pages on the GPU; fp8 caches are dequantised exactly."""
+    if w.kv_cache_dtype == "auto":
+        return _torch_fp32_reference(w)
+    dt = O.FP8_FORMATS[w.kv_cache_dtype][0]
+    kc = (w.key_cache.view(dt).float() * w.k_scale).to(torch.float32)
+    vc = (w.value_cache.view(dt).float() * w.v_scale).to(torch.float32)
+    import dataclasses
+    return _torch_fp32_reference(dataclasses.replace(w, key_cache=kc, value_cache=vc))
+
+
+@pytest.mark.parametrize("seed", range(128))
+def test_random_shapes_against_fp32_attention(seed):
+    """Seeded random draws over the argument space (batch size, head grouping, head size, block
+    size, cache type, length distribution, entry point): every scheduling regime of the decode
+    kernel (one item per warp, strided items, tickets; paired blocks; deep rings) shows up."""
+    rng = np.random.default_rng(1000 + seed)
+    hkv = int(rng.choice([1, 2, 4, 8]))
+    group = int(rng.choice([1, 2, 4, 5, 8, 12, 16]))
+    d = int(rng.choice([32, 64, 80, 96, 112, 128, 192, 256]))
+    bs = int(rng.choice([16, 32]))
+    kv = str(rng.choice(["auto", "fp8", "fp8_e5m2"]))
+    if kv != "auto" and d % 16:
+        d = 128
+    s = int(rng.choice([1, 2, 5, 17, 64, 200]))
+    max_len = int(rng.choice([20, 300, 1500, 5000]))
+    if s * hkv * max_len * d > 3e8:
+        max_len = 300
+    kind = int(rng.integers(3))
+    if kind == 0:
+        lens = rng.integers(1, max_len + 1, size=s)
+    elif kind == 1:
+        lens = np.full(s, max_len)
+    else:
+        lens = np.clip(np.round(rng.lognormal(np.log(max_len) - 1.5, 1.0, size=s)), 1, max_len).astype(np.int64)
+    lens[rng.integers(s)] = max_len
+    w = W.make_decode("fuzz", num_seqs=s, num_heads=hkv * group, num_kv_heads=hkv, head_size=d,
+                      block_size=bs, lens=lens, dtype=torch.bfloat16 if seed % 3 else torch.float16,
+                      kv_cache_dtype=kv, device=DEV, seed=seed, rng=rng)
+    w.query.mul_(4.0)
+    want = _torch_reference_any(w)
+    tol = 2e-2 if kv != "auto" else 1e-2
+    for version in ("v1", "v2"):
+        got = W.run_attention(w, version=version).float()
+        torch.cuda.synchronize()
+        assert capi.device_status() == 0
+        torch.testing.assert_close(got, want, atol=tol, rtol=tol,
+                                   msg=lambda m: f"{version} hkv={hkv} G={group} D={d} B={bs} kv={kv} "
+                                                 f"S={s} max_len={max_len} kind={kind}: {m}")

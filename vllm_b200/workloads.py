@@ -124,16 +124,17 @@ def _uniform_(t: torch.Tensor, lo: float, hi: float, gen: torch.Generator) -> No
         flat[a:b] = tmp.to(t.dtype)
 
 
-def _fp8_normal_(t: torch.Tensor, scale: float, gen: torch.Generator) -> None:
-    """Fills a uint8 tensor with e4m3 codes of N(0,1)/scale (RNE, saturating)."""
+def _fp8_normal_(t: torch.Tensor, scale: float, gen: torch.Generator, e5m2: bool = False) -> None:
+    """Fills a uint8 tensor with e4m3 (or e5m2) codes of N(0,1)/scale (RNE, saturating)."""
     flat = t.view(-1)
     step = 1 << 27
+    fmax, dt = (57344.0, torch.float8_e5m2) if e5m2 else (448.0, torch.float8_e4m3fn)
     for a in range(0, flat.numel(), step):
         b = min(flat.numel(), a + step)
         tmp = torch.empty(b - a, dtype=torch.float32, device=t.device)
         tmp.normal_(0.0, 1.0, generator=gen)
-        tmp.div_(scale).clamp_(-448.0, 448.0)
-        flat[a:b] = tmp.to(torch.float8_e4m3fn).view(torch.uint8)
+        tmp.div_(scale).clamp_(-fmax, fmax)
+        flat[a:b] = tmp.to(dt).view(torch.uint8)
 
 
 def make_decode(name: str, *, num_seqs: int, num_heads: int, num_kv_heads: int, head_size: int,
@@ -155,9 +156,11 @@ def make_decode(name: str, *, num_seqs: int, num_heads: int, num_kv_heads: int, 
     vc = torch.empty((nb, num_kv_heads, head_size, block_size), dtype=cdt, device=dev)
     if fp8:
         # per-tensor scales as a caller would compute them: amax / 448 of N(0,1) data
-        ks, vs = 5.3 / 448.0, 5.2 / 448.0
-        _fp8_normal_(kc, ks, gen)
-        _fp8_normal_(vc, vs, gen)
+        e5m2 = kv_cache_dtype == "fp8_e5m2"
+        fmax = 57344.0 if e5m2 else 448.0
+        ks, vs = 5.3 / fmax, 5.2 / fmax
+        _fp8_normal_(kc, ks, gen, e5m2)
+        _fp8_normal_(vc, vs, gen, e5m2)
     else:
         ks = vs = 1.0
         _uniform_(kc, -amp, amp, gen)
