@@ -180,3 +180,57 @@ def test_fp8_quantiser_fp32_inputs_ties_and_odd_scales():
             bad = torch.nonzero(dst.cpu() != want).flatten()
             assert bad.numel() == 0, (kv, scale, bad.numel(), x[bad[:4]].tolist(),
                                       dst.cpu()[bad[:4]].tolist(), want[bad[:4]].tolist())
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_reshape_and_cache_random_shapes_and_slot_patterns(seed):
+    """Seeded random draws: token counts around the 16-token tile, head counts and sizes that make
+    the per-token item count smaller or larger than a CTA, prefill-like consecutive slots (the
+    transposing fast path), decode-like scattered slots, padding tokens, both layouts."""
+    rng = np.random.default_rng(500 + seed)
+    dtype = [torch.bfloat16, torch.float16, torch.float32][int(rng.integers(3))]
+    kv = ["auto", "fp8", "fp8_e5m2"][int(rng.integers(3))]
+    fp8 = kv != "auto"
+    block_size = int(rng.choice([8, 16, 32]))
+    H = int(rng.choice([1, 2, 3, 8, 16]))
+    head_size = int(rng.choice([32, 64, 128, 256]))
+    T = int(rng.choice([1, 15, 16, 17, 31, 48, 100, 257]))
+    NB = (T + block_size - 1) // block_size + 40
+    pattern = int(rng.integers(3))
+    if pattern == 0:    # prefill: consecutive slots from a block boundary
+        start = int(rng.integers(0, 20)) * block_size
+        slots = np.arange(start, start + T, dtype=np.int64)
+    elif pattern == 1:  # decode: scattered
+        slots = rng.permutation(NB * block_size)[:T].astype(np.int64)
+    else:               # chunks of consecutive slots at odd offsets, with padding tokens
+        slots = np.full(T, -1, dtype=np.int64)
+        pos, t = int(rng.integers(0, 7)), 0
+        while t < T:
+            n = int(min(T - t, rng.integers(1, 40)))
+            slots[t:t + n] = np.arange(pos, pos + n)
+            pos += n + int(rng.integers(0, 50))
+            t += n + int(rng.integers(0, 3))
+        slots = np.where(slots >= NB * block_size, -1, slots)
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    key = torch.randn(T, H, head_size, device=DEV, generator=g).mul(2).to(dtype)
+    val = torch.randn(T, H, head_size, device=DEV, generator=g).mul(2).to(dtype)
+    slots_t = torch.from_numpy(slots).to(DEV)
+    ks = torch.tensor(float(rng.choice([1.0, 0.0173, 0.37, 2.0 ** -61])), device=DEV)
+    vs = torch.tensor(float(rng.choice([1.0, 0.0291, 0.11])), device=DEV)
+    cdt = torch.uint8 if fp8 else dtype
+    same = lambda a, b: torch.equal(a.cpu().contiguous().view(torch.uint8), b.cpu().contiguous().view(torch.uint8))
+    # x layout
+    x = 16 // (1 if fp8 else key.element_size())
+    kc = torch.zeros(NB, H, head_size // x, block_size, x, dtype=cdt, device=DEV)
+    vc = torch.zeros(NB, H, head_size, block_size, dtype=cdt, device=DEV)
+    ops.reshape_and_cache(key, val, kc, vc, slots_t, kv, ks, vs)
+    kco, vco = torch.zeros_like(kc, device="cpu"), torch.zeros_like(vc, device="cpu")
+    O.reshape_and_cache(key.cpu(), val.cpu(), kco, vco, slots_t.cpu(), kv, float(ks), float(vs))
+    assert same(kc, kco) and same(vc, vco), ("x layout", dtype, kv, block_size, H, head_size, T, pattern)
+    # flash layout
+    kf = torch.zeros(NB, block_size, H, head_size, dtype=cdt, device=DEV)
+    vf = torch.zeros_like(kf)
+    ops.reshape_and_cache_flash(key, val, kf, vf, slots_t, kv, ks, vs)
+    kfo, vfo = torch.zeros(kf.shape, dtype=cdt), torch.zeros(vf.shape, dtype=cdt)
+    O.reshape_and_cache_flash(key.cpu(), val.cpu(), kfo, vfo, slots_t.cpu(), kv, float(ks), float(vs))
+    assert same(kf, kfo) and same(vf, vfo), ("flash layout", dtype, kv, block_size, H, head_size, T, pattern)
