@@ -3,12 +3,15 @@
 // (csrc/attention/attention_kernels.cuh:81-491).
 //
 // Design (bandwidth first; the KV cache is read exactly once):
-//   * One persistent CTA per SM.  Every WARP is an independent worker: it pulls a
-//     work item (sequence, kv head, 512-token partition) from a global ticket,
-//     streams that item's KV pages through its own ring of shared-memory stages
+//   * One persistent CTA per SM.  Every WARP is an independent worker: it owns work
+//     items (sequence, kv head, partition of 64..512 tokens) - dealt out by a fixed
+//     stride when there are few, pulled from a global ticket counter when there are
+//     many - streams an item's KV pages through its own ring of shared-memory slots
 //     and writes the item's result itself.  There is no CTA-wide barrier after
 //     set-up, and a warp keeps prefetching pages of its NEXT item while it
 //     finishes the current one, so the pipeline never drains.
+//   * The warp that delivers the last partial of a sequence merges all of them
+//     (no second launch, nobody waits).
 //   * A KV page (one block of one kv head) is contiguous in both cache layouts:
 //     K [D/x][B][x] and V [D][B].  Each is fetched with ONE 1-D bulk async copy
 //     (cp.async.bulk, completion on an mbarrier; no cluster multicast).
