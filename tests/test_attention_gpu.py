@@ -432,3 +432,25 @@ def test_random_shapes_against_fp32_attention(seed):
         torch.testing.assert_close(got, want, atol=tol, rtol=tol,
                                    msg=lambda m: f"{version} hkv={hkv} G={group} D={d} B={bs} kv={kv} "
                                                  f"S={s} max_len={max_len} kind={kind}: {m}")
+
+
+def test_batches_beyond_the_partition_table_run_unsplit():
+    """v2 on more sequences than the in-kernel partition table holds (12k): the kernel ignores
+    the caller's scratch and runs every sequence as one item."""
+    S = 13000
+    rng = np.random.default_rng(77)
+    lens = rng.integers(1, 700, size=S)
+    lens[5] = 1000
+    w = W.make_decode("huge", num_seqs=S, num_heads=2, num_kv_heads=1, head_size=32, block_size=16,
+                      lens=lens, dtype=torch.bfloat16, kv_cache_dtype="auto", device=DEV, seed=77, rng=rng)
+    w.query.mul_(4.0)
+    got2 = W.run_attention(w, version="v2")
+    got1 = W.run_attention(w, version="v1")
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    assert torch.equal(got1, got2)
+    pick = [0, 5, 6, 4095, 4096, 12287, 12288, S - 1] + rng.integers(0, S, size=40).tolist()
+    import dataclasses
+    idx = torch.tensor(pick, device=DEV)
+    sub = dataclasses.replace(w, query=w.query[idx], block_tables=w.block_tables[idx], seq_lens=w.seq_lens[idx])
+    torch.testing.assert_close(got2[idx].float(), _torch_fp32_reference(sub), atol=1e-2, rtol=1e-2)

@@ -516,6 +516,12 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
         }
       }
     }
+    // The partition table of a split launch lives in shared memory (4 bytes per sequence).
+    // Batches it cannot hold have more than enough sequences to fill the GPU unsplit.
+    if (split && size_t((p.num_seqs + 1 + 3) & ~3) * 4 > 48 * 1024) {
+      split = false;
+      p.max_partitions = 0;
+    }
     // lengths beyond what the scratch has partitions for are ignored, like the reference's v2
     // grid ignores partitions beyond max_num_partitions
     p.len_cap = split ? int(std::min<int64_t>(int64_t(p.max_partitions) * p.part_tokens, INT32_MAX))
