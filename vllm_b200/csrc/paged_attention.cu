@@ -493,7 +493,28 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
       while (pt > 64 && parts_of(pt / 2) <= max_parts &&
              units * parts_of(pt / 2) <= per_warp * warps_total)
         pt /= 2;
+      // fp8 caches: a warp's time goes into its own instruction chain (every cache byte is
+      // converted before the MMA), not into waiting for HBM, so the fixed cost of an item
+      // (~7 us of round trips that nothing overlaps) counts.  Measured on B200 with sequences
+      // of equal length, about 1.7 items per warp is the optimum (config 3: 0.376 ms with
+      // 512-token partitions, 0.345 ms with 2048); with mixed lengths the count estimated from
+      // max_seq_len is about twice the real one and that point is already too coarse.  So:
+      // coarsen while the estimate keeps at least `kMinItemsPerWarp` items per warp, and never
+      // beyond 2048 tokens (larger items of unequal length lengthen the tail of big batches).
+      // 16-bit caches stay at 512 (config 2 loses 5 % with 1024).
+      if (es == 1 && pt == kPartitionTokens) {
+        int min_items_per_warp = 3;
+        if (const char* e = getenv("B200PA_TUNE_FP8_ITEMS")) min_items_per_warp = atoi(e);
+        while (pt < 2048 && parts_of(pt) > 1 &&
+               units * parts_of(2 * pt) >= min_items_per_warp * warps_total)
+          pt *= 2;
+      }
       if (const char* e = getenv("B200PA_TUNE_PT")) pt = atoi(e);  // 0: no library split
+      if (split && pt > kPartitionTokens) {
+        // the caller's scratch has a partition slot per 512 tokens: coarser partitions use the
+        // first ceil(len / pt) of them
+        p.part_tokens = pt;
+      }
       if (pt > 0 && (!split || pt < kPartitionTokens)) {
         auto up = [](int64_t v) { return (v + 255) & ~int64_t(255); };
         auto need_of = [&](int t) {
@@ -501,6 +522,8 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
           return 2 * up(n * 4) + up(n * a->head_size * 2);
         };
         while (pt < kPartitionTokens && need_of(pt) > int64_t(kV1ScratchBytes)) pt *= 2;
+        // fp8 (see above): rather fewer, larger partitions than none at all
+        while (es == 1 && parts_of(pt) > 1 && need_of(pt) > int64_t(kV1ScratchBytes)) pt *= 2;
         const int64_t parts = parts_of(pt);
         const int64_t stat = up(int64_t(p.num_seqs) * p.num_heads * parts * 4);
         unsigned char* ws = ((!split || pt < kPartitionTokens) && parts > 1 &&
@@ -524,7 +547,10 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
     }
     // lengths beyond what the scratch has partitions for are ignored, like the reference's v2
     // grid ignores partitions beyond max_num_partitions
-    p.len_cap = split ? int(std::min<int64_t>(int64_t(p.max_partitions) * p.part_tokens, INT32_MAX))
+    // (the caller's scratch covers max_partitions * 512 tokens whatever the partition size)
+    const int slot_tokens = p.exp_sums == a->exp_sums ? std::min(p.part_tokens, kPartitionTokens)
+                                                      : p.part_tokens;
+    p.len_cap = split ? int(std::min<int64_t>(int64_t(p.max_partitions) * slot_tokens, INT32_MAX))
                       : INT32_MAX;
     p.use_table = split ? 1 : 0;
     const size_t table_bytes = p.use_table ? size_t((p.num_seqs + 1 + 3) & ~3) * 4 : 0;
