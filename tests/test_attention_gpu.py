@@ -454,3 +454,29 @@ def test_batches_beyond_the_partition_table_run_unsplit():
     idx = torch.tensor(pick, device=DEV)
     sub = dataclasses.replace(w, query=w.query[idx], block_tables=w.block_tables[idx], seq_lens=w.seq_lens[idx])
     torch.testing.assert_close(got2[idx].float(), _torch_fp32_reference(sub), atol=1e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("version", ["v1", "v2"])
+def test_fp8_large_batch_takes_coarser_partitions(version):
+    """A large fp8 batch makes the host pick partitions of more than 512 tokens (v2: inside the
+    caller's 512-token scratch slots; v1: in the library workspace).  Lengths straddle the
+    coarser partition boundaries."""
+    S = 224
+    rng = np.random.default_rng(91)
+    lens = rng.integers(2900, 4097, size=S)
+    lens[:6] = [4096, 1, 1024, 1025, 2048, 3073]
+    w = W.make_decode("coarse", num_seqs=S, num_heads=32, num_kv_heads=8, head_size=64, block_size=16,
+                      lens=lens, dtype=torch.bfloat16, kv_cache_dtype="fp8", device=DEV, seed=91, rng=rng,
+                      max_seq_len=4096)
+    w.query.mul_(4.0)
+    got = W.run_attention(w, version=version)
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    pick = list(range(8)) + rng.integers(0, S, size=24).tolist()
+    idx = torch.tensor(pick, device=DEV)
+    import dataclasses
+    sub = dataclasses.replace(w, query=w.query[idx], block_tables=w.block_tables[idx], seq_lens=w.seq_lens[idx])
+    torch.testing.assert_close(got[idx].float(), _torch_reference_any(sub), atol=2e-2, rtol=2e-2)
+    # every sequence: the two entry points (different scratch, same arithmetic) agree
+    other = W.run_attention(w, version="v1" if version == "v2" else "v2")
+    torch.testing.assert_close(got.float(), other.float(), atol=2e-3, rtol=1e-2)
