@@ -81,7 +81,8 @@ int b200pa_kv_dtype_from_string(const char* kv_cache_dtype);
  *   alibi_slopes [num_heads] float32 or NULL
  *   k_scale, v_scale : device pointers to ONE float each (may be NULL when
  *                kv_dtype == B200PA_KV_AUTO)
- * v2 scratch, owned by the caller, contents unspecified after the call:
+ * v2 scratch, owned by the caller, contents unspecified after the call (the library lays its
+ * partial results out in it as it sees fit):
  *   exp_sums, max_logits [num_seqs, num_heads, max_num_partitions] float32
  *   tmp_out              [num_seqs, num_heads, max_num_partitions, head_size] (query dtype)
  *   max_num_partitions = ceil(max_seq_len / 512)
@@ -139,18 +140,25 @@ typedef struct b200pa_attn_args {
 } b200pa_attn_args;
 
 /* Replaces paged_attention_v1 (csrc/attention/paged_attention_v1.cu:160-182).  No scratch
- * argument, as in the reference; long sequences of small batches are nevertheless split
- * across work items through a 32 MiB workspace inside the library (partials of at most
- * that size, else one work item per sequence and kv head).  That workspace is shared by
- * all calls on a device: calls that overlap on the GPU (different streams without an
- * ordering between them) must not both be small-batch attention calls. */
+ * argument, as in the reference; sequences are nevertheless cut into pieces that different
+ * warps process (by equal numbers of cache blocks, from the real lengths), with the partial
+ * results kept in a workspace inside the library (60 MiB per GPU that loads it) and merged in
+ * the same launch.  Calls may overlap on the GPU like the reference's: every stream gets its
+ * own part of that workspace - 32 MiB for the first stream used on a device, 4 MiB for each of
+ * up to seven more (a least-recently-used slot is reassigned after that; more than eight
+ * streams calling concurrently are not kept apart).  A batch whose partials do not fit its
+ * stream's part is cut more coarsely, or not at all.  A kernel node captured into a CUDA graph
+ * keeps the workspace part of the stream it was captured on. */
 int b200pa_paged_attention_v1(const b200pa_attn_args* args, void* stream);
 
 /* Replaces paged_attention_v2 + its reduce kernel
  * (csrc/attention/paged_attention_v2.cu:167-192, attention_kernels.cuh:559-664):
- * split-KV over 512-token partitions using the caller's scratch, merged inside the same
- * kernel.  Batches too small to fill the GPU with 512-token partitions are split finer
- * through the library workspace described at b200pa_paged_attention_v1 instead. */
+ * split-KV with the partial results in the caller's scratch, merged inside the same kernel.
+ * The scratch is used as max_num_partitions slots per (sequence, head); which tokens a slot
+ * covers is decided in the kernel (equal numbers of cache blocks per warp), not fixed at 512.
+ * Few, long sequences need more slots per sequence than ceil(max_seq_len / 512) to occupy the
+ * GPU; such calls keep their partials in the workspace described at b200pa_paged_attention_v1
+ * instead and leave the caller's scratch untouched. */
 int b200pa_paged_attention_v2(const b200pa_attn_args* args, void* stream);
 
 /*
@@ -163,14 +171,16 @@ int b200pa_paged_attention_v2(const b200pa_attn_args* args, void* stream);
  * at start-up, where a later cudaMalloc can fail.  This entry point allocates
  * nothing (no cudaMalloc / cudaFree, no allocating library call): the split-KV
  * scratch is a 32 MiB array built into the library, resident on every GPU that
- * loads it until the process exits.
+ * loads it until the process exits (in addition to the 60 MiB workspace of
+ * b200pa_paged_attention_v1, which this entry point does not use).
  *
  *   - args->exp_sums, max_logits, tmp_out and max_num_partitions are ignored
  *     (may be NULL / 0); everything else is as for b200pa_paged_attention_v2.
  *   - Limit: num_seqs * num_heads * ceil(max_seq_len/512) * (8 + head_size *
  *     sizeof(query element)) bytes, each of the three regions rounded up to
  *     256 bytes, must fit 32 MiB; larger problems return B200PA_EINVAL with a
- *     message and launch nothing.
+ *     message and launch nothing.  Room that a smaller problem leaves is used for
+ *     more partial slots per sequence.
  *   - The first call on a device resolves the array's device address; make that
  *     call before any stream capture.
  *   - All calls on one device share the array.  Calls that may overlap on the

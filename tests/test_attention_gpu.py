@@ -480,3 +480,93 @@ def test_fp8_large_batch_takes_coarser_partitions(version):
     # every sequence: the two entry points (different scratch, same arithmetic) agree
     other = W.run_attention(w, version="v1" if version == "v2" else "v2")
     torch.testing.assert_close(got.float(), other.float(), atol=2e-3, rtol=1e-2)
+
+
+@pytest.mark.parametrize("version", ["v1", "v2"])
+def test_config1_exact_shape(version, ref_cuda_ops):
+    """The small-batch configuration as stated: 8 sequences, 32 query = 32 KV heads, head size
+    128, block size 16, bf16, lengths U{1..1024}, 4096 blocks, every block-table row sampled on
+    its own.  Oracle in both arithmetics, and the reference's own CUDA kernel on the same tensors."""
+    w = W.config1(DEV)
+    assert (w.num_seqs, w.num_heads, w.num_kv_heads, w.head_size, w.block_size) == (8, 32, 32, 128, 16)
+    assert w.key_cache.shape[0] == 4096 and int(w.seq_lens.max()) <= 1024
+    out = check(w, version).clone()
+    # and away from the near-uniform softmax that the stated value range produces
+    w.query.mul_(16.0)
+    sharp = check(w, version)
+    if ref_cuda_ops is not None:
+        r = torch.empty_like(w.query)
+        tail = (w.query, w.key_cache, w.value_cache, w.num_kv_heads, w.scale, w.block_tables,
+                w.seq_lens, w.block_size, w.max_seq_len, None, "auto", w.k_scale, w.v_scale,
+                0, 0, 0, 64, 0)
+        if version == "v1":
+            ref_cuda_ops[0].paged_attention_v1(r, *tail)
+        else:
+            e, m, t = w.scratch()
+            ref_cuda_ops[0].paged_attention_v2(r, e, m, t, *tail)
+        torch.testing.assert_close(sharp.float(), r.float(), atol=1e-2, rtol=1e-2)
+    assert torch.isfinite(out.float()).all()
+
+
+@pytest.mark.parametrize("version", ["v1", "v2"])
+def test_calls_overlapping_on_two_streams_do_not_share_partials(version):
+    """The reference ops may be called concurrently on different streams (each call owns its
+    scratch).  Here v1 - and v2 with few, long sequences - keeps split-KV partials in a
+    workspace of the library, so every stream has to get its own part of it.  Two different
+    small batches of long sequences run on two streams at the same time, 50 times; each must
+    come out exactly as it does alone."""
+    ws = []
+    for seed, n in ((61, 3), (62, 2)):
+        rng = np.random.default_rng(seed)
+        lens = rng.integers(9000, 12001, size=n)
+        w = W.make_decode("two-streams", num_seqs=n, num_heads=8, num_kv_heads=2, head_size=128,
+                          block_size=16, lens=lens, dtype=torch.bfloat16, kv_cache_dtype="auto",
+                          device=DEV, seed=seed, rng=rng)
+        w.query.mul_(8.0)
+        ws.append(w)
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    outs = [[torch.empty_like(w.query) for _ in range(50)] for w in ws]
+    scratch = [w.scratch() for w in ws]
+    for st in streams:
+        st.wait_stream(torch.cuda.current_stream())
+    alone = []
+    for k in (0, 1):  # one at a time, each on the stream it will use below
+        with torch.cuda.stream(streams[k]):
+            alone.append(W.run_attention(ws[k], version=version, scratch=scratch[k]).clone())
+        torch.cuda.synchronize()
+    for w, a in zip(ws, alone):
+        want = oracle_out(w, "f64")
+        torch.testing.assert_close(a.cpu().double(), want, atol=1e-2, rtol=1e-2)
+    for i in range(50):
+        for k in (0, 1):
+            with torch.cuda.stream(streams[k]):
+                W.run_attention(ws[k], out=outs[k][i], version=version, scratch=scratch[k])
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    for k in (0, 1):
+        for i in range(50):
+            assert torch.equal(outs[k][i], alone[k]), f"stream {k}, call {i}"
+
+
+def test_skewed_lengths_split_by_equal_block_counts():
+    """One very long sequence among many short ones, few sequences per kv head and the other
+    way round: the split is made by block count across sequence boundaries, so ranges start
+    and end in the middle of sequences, cover several short ones, or hold a single block."""
+    rng = np.random.default_rng(404)
+    for hq, hkv, lens in (
+        (8, 2, [30000] + [17] * 40 + [1, 0, 16, 33]),
+        (32, 8, [5, 4000, 3, 2, 9000, 1]),
+        (4, 4, list(rng.integers(1, 60, size=300))),
+        (16, 1, [12000, 12001, 11999]),
+    ):
+        lens = np.array(lens)
+        w = W.make_decode("skew", num_seqs=len(lens), num_heads=hq, num_kv_heads=hkv, head_size=128,
+                          block_size=16, lens=lens, dtype=torch.bfloat16, kv_cache_dtype="auto",
+                          device=DEV, seed=7, rng=rng)
+        w.query.mul_(8.0)
+        want = _torch_fp32_reference(w)
+        for version in ("v1", "v2"):
+            got = W.run_attention(w, version=version).float()
+            torch.cuda.synchronize()
+            assert capi.device_status() == 0
+            torch.testing.assert_close(got, want, atol=1e-2, rtol=1e-2)

@@ -37,6 +37,71 @@ def test_backend_static_interface():
         B200PagedAttentionImpl(8, 128, 0.1, 2, sliding_window=128)
 
 
+def test_metadata_builder_has_the_engine_facing_signature():
+    """The engine constructs builders as Builder(kv_cache_spec, layer_names, vllm_config, device)
+    and calls build(common_prefix_len, common_attn_metadata, fast_build)
+    (vllm/v1/attention/backends/utils.py:255-330, rocm_attn.py:65-150)."""
+    import inspect
+    assert list(inspect.signature(B200PagedAttentionMetadataBuilder.__init__).parameters) == [
+        "self", "kv_cache_spec", "layer_names", "vllm_config", "device"]
+    assert list(inspect.signature(B200PagedAttentionMetadataBuilder.build).parameters) == [
+        "self", "common_prefix_len", "common_attn_metadata", "fast_build"]
+    b = B200PagedAttentionMetadataBuilder(types.SimpleNamespace(block_size=32), ["l0", "l1"], None, "cpu")
+    assert b.block_size == 32 and b.layer_names == ["l0", "l1"]
+    assert B200PagedAttentionMetadataBuilder.get_cudagraph_support(None, None) == "ALWAYS"
+    common = types.SimpleNamespace(
+        query_start_loc=torch.tensor([0, 1, 2], dtype=torch.int32), seq_lens=torch.tensor([7, 9], dtype=torch.int32),
+        num_reqs=2, num_actual_tokens=2, max_query_len=1, max_seq_len=9,
+        block_table_tensor=torch.zeros(2, 1, dtype=torch.int32), slot_mapping=torch.tensor([6, 40]))
+    md = b.build(0, common, fast_build=True)
+    assert md.block_table is common.block_table_tensor and md.max_seq_len == 9 and md.use_cascade is False
+    cap = b.build_for_cudagraph_capture(common)
+    assert cap.seq_lens.tolist() == [1, 1]
+    with pytest.raises(NotImplementedError):
+        b.build(16, common)
+
+
+def test_plugin_repoints_the_wrappers_of_a_custom_ops_module():
+    """vllm_b200.plugin.register() against a stand-in for vllm._custom_ops and for the backend
+    registry: the wrappers of this path are replaced by functions of the same name, everything
+    else is left alone, the backend is registered as CUSTOM, and a second call changes nothing."""
+    import sys
+
+    from vllm_b200 import _custom_ops as b200
+    from vllm_b200 import plugin
+
+    def _orig(*a, **k):
+        raise AssertionError("the reference wrapper was called")
+
+    fake_ops = types.ModuleType("fake_vllm_custom_ops")
+    for name in plugin.OPS:
+        setattr(fake_ops, name, _orig)
+    fake_ops.rms_norm = _orig  # not on this path
+    registered = []
+    fake_reg = types.ModuleType("fake_vllm_registry")
+    fake_reg.AttentionBackendEnum = types.SimpleNamespace(CUSTOM="CUSTOM")
+    fake_reg.register_backend = lambda which, path: registered.append((which, path))
+    sys.modules["fake_vllm_custom_ops"], sys.modules["fake_vllm_registry"] = fake_ops, fake_reg
+    try:
+        for _ in range(2):
+            done = plugin.register("fake_vllm_custom_ops", "fake_vllm_registry")
+            assert set(done["ops"]) == set(plugin.OPS) and done["backend"] is True
+            for name in ("paged_attention_v1", "paged_attention_v2", "reshape_and_cache",
+                         "reshape_and_cache_flash", "convert_fp8"):
+                assert getattr(fake_ops, name) is getattr(b200, name)
+            assert fake_ops.rms_norm is _orig
+        assert registered[0] == ("CUSTOM", "vllm_b200.backend.B200PagedAttentionBackend")
+        import importlib
+        mod, cls = registered[0][1].rsplit(".", 1)
+        assert getattr(importlib.import_module(mod), cls) is B200PagedAttentionBackend
+        plugin.unregister("fake_vllm_custom_ops")
+        assert fake_ops.paged_attention_v1 is _orig
+        # without a registry module only the wrappers are patched
+        assert plugin.register("fake_vllm_custom_ops", "no_such_registry_module")["backend"] is False
+    finally:
+        del sys.modules["fake_vllm_custom_ops"], sys.modules["fake_vllm_registry"]
+
+
 def _dense_causal(q, k, v, scale, g):
     """q [n, Hq, D] are the last n positions of a sequence whose keys are k [L, Hkv, D]."""
     L, n = k.shape[0], q.shape[0]
@@ -61,7 +126,7 @@ def test_prefill_chunk_and_decode_session(kv_cache_dtype):
     kv_cache = torch.zeros(shape, dtype=torch.uint8 if kv_cache_dtype == "fp8" else dtype, device=dev)
     layer = types.SimpleNamespace(_k_scale=torch.tensor(0.05 if kv_cache_dtype == "fp8" else 1.0, device=dev),
                                   _v_scale=torch.tensor(0.04 if kv_cache_dtype == "fp8" else 1.0, device=dev))
-    builder = B200PagedAttentionMetadataBuilder(B)
+    builder = B200PagedAttentionMetadataBuilder(types.SimpleNamespace(block_size=B), ["layer.0"], None, dev)
     gen = torch.Generator(device=dev).manual_seed(0)
     rng = np.random.default_rng(0)
     nreq = 3
@@ -91,9 +156,13 @@ def test_prefill_chunk_and_decode_session(kv_cache_dtype):
             hist_v[r] = torch.cat([hist_v[r].to(vv.dtype), vv])
             off += ln
         lens = torch.tensor([h.shape[0] for h in hist_k], dtype=torch.int32, device=dev)
-        md = builder.build(num_actual_tokens=n, max_query_len=max(step_lens), query_start_loc=qsl,
-                           max_seq_len=int(lens.max()), seq_lens=lens, block_table=bt,
-                           slot_mapping=torch.cat(slots))
+        # what the engine hands every builder (CommonAttentionMetadata, utils.py:53-95)
+        common = types.SimpleNamespace(
+            query_start_loc=qsl, query_start_loc_cpu=qsl.cpu(), seq_lens=lens, seq_lens_cpu=lens.cpu(),
+            num_computed_tokens_cpu=(lens.cpu() - torch.tensor(step_lens)), num_reqs=nreq,
+            num_actual_tokens=n, max_query_len=max(step_lens), max_seq_len=int(lens.max()),
+            block_table_tensor=bt, slot_mapping=torch.cat(slots), causal=True)
+        md = builder.build(0, common)
         out = torch.empty(n + 3, Hq * D, device=dev, dtype=dtype)  # padded like a CUDA-graph batch
         impl.forward(layer, torch.cat([q, q[:3]]), torch.cat([k, k[:3]]), torch.cat([v, v[:3]]),
                      kv_cache, md, output=out)

@@ -57,6 +57,9 @@ def _attn(**kw):
     (dict(q_dtype=7), "Unsupported input type"),
     (dict(kv_dtype=9), "Unsupported data type of kv cache"),
     (dict(num_heads=7), "not a multiple"),
+    # an fp8 cache keeps 16 head dimensions together (x = 16): head size 120 cannot exist in it
+    (dict(head_size=120, kv_dtype=capi.KV_FP8_E4M3), "not a multiple of x = 16"),
+    (dict(head_size=120, kv_dtype=capi.KV_FP8_E5M2), "not a multiple of x = 16"),
     (dict(blocksparse_vert_stride=2, blocksparse_block_size=24), "blocksparse_block_size"),
     (dict(), "null tensor pointer"),
 ])

@@ -106,6 +106,30 @@ def test_full_size_kv_write_round_trip():
     assert torch.equal(w.key_cache, snap_k) and torch.equal(w.value_cache, snap_v)
 
 
+def test_config5_full_batch():
+    """config 5 as stated: 2048 sequences, 64 query / 8 KV heads, block size 32, fp8-e4m3,
+    lengths U{1024..8192} (about 19 GB of cache).  The oracle on a subsample of sequences,
+    agreement of v1 (library workspace) and v2 (caller scratch), exact linearity in v_scale."""
+    w = W.config5(DEV)
+    assert w.num_seqs == 2048 and w.block_size == 32 and w.kv_cache_dtype == "fp8"
+    w.query.mul_(16.0)
+    scratch = w.scratch()
+    out2 = W.run_attention(w, version="v2", scratch=scratch).clone()
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    assert torch.isfinite(out2.float()).all()
+    out1 = W.run_attention(w, version="v1")
+    torch.testing.assert_close(out1.float(), out2.float(), atol=2e-2, rtol=2e-2)
+    lens = w.seq_lens.cpu().numpy()
+    rng = np.random.default_rng(5)
+    seqs = sorted({0, 2047, int(lens.argmin()), int(lens.argmax())} | set(rng.integers(0, 2048, size=4).tolist()))
+    _oracle_subsample(w, out2, seqs, 2e-2)
+    w.v_scale.mul_(2.0)
+    out_lin = W.run_attention(w, version="v2", scratch=scratch)
+    assert torch.equal(out_lin.float(), out2.float() * 2.0)
+    w.v_scale.mul_(0.5)
+
+
 def test_config5_shape_subsample():
     """config 5 shape (fp8, block size 32, 64/8 heads) at a quarter of the batch: oracle on
     four sequences, v1/v2 agreement."""

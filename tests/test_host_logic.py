@@ -16,6 +16,7 @@ def _norm(s):
 
 
 def test_schemas_equal_the_reference_declarations():
+    ops.claim_reference_names()
     # csrc/torch_bindings.cpp:52-76, :687-704, :716-719 of the reference
     want_v1 = ("paged_attention_v1(Tensor! out, Tensor query, Tensor key_cache, Tensor value_cache, "
                "int num_kv_heads, float scale, Tensor block_tables, Tensor seq_lens, int block_size, "
@@ -140,3 +141,24 @@ def test_token_ranges_cover_every_token_once_at_block_boundaries():
                 prev_end = b1
             assert np.array_equal(total, lens)
             assert np.array_equal(prev_end, (lens + block_size - 1) // block_size)
+
+
+def test_reference_names_are_claimed_on_request_and_never_twice():
+    """Loading the package defines torch.ops._C_b200.* only.  The reference's own names are
+    registered by an explicit call (so that a vLLM extension imported later can still define
+    them itself), once: a second call finds them taken and claims nothing."""
+    import subprocess
+    import sys
+    code = (
+        "import torch\n"
+        "from vllm_b200 import _custom_ops as ops\n"
+        "has = lambda: hasattr(torch.ops._C, 'paged_attention_v1') and hasattr(torch.ops._C_cache_ops, 'reshape_and_cache')\n"
+        "a = has()\n"
+        "n1 = ops.claim_reference_names()\n"
+        "b = has()\n"
+        "n2 = ops.claim_reference_names()\n"
+        "print(a, n1, b, n2)\n")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True,
+                       cwd=str(__import__("pathlib").Path(__file__).resolve().parents[1]))
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert r.stdout.split() == ["False", "8", "True", "0"]

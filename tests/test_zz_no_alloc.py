@@ -1,8 +1,9 @@
 """b200pa_paged_attention_v2_noalloc: the split-KV decode for callers that have no
 device memory to lend (a bare C host without an allocator; a server whose HBM is
-already committed to the KV pool).  It must produce what b200pa_paged_attention_v2
-produces with caller-owned scratch, call after call, although every call reuses
-the same built-in buffer and finds the previous call's partials in it.
+already committed to the KV pool).  It must produce the oracle's result - and what
+b200pa_paged_attention_v2 produces with caller-owned scratch - call after call,
+although every call reuses the same built-in buffer and finds the previous call's
+partials in it.
 
 Collected last on purpose (file name), so a failure here cannot hide other tests
 from a run that stops at the first failure.  Both entry points are called through
@@ -12,6 +13,7 @@ import numpy as np
 import pytest
 import torch
 
+from oracle import paged_oracle as O
 from vllm_b200 import capi
 from vllm_b200 import workloads as W
 
@@ -39,28 +41,54 @@ def _args(w, out, scratch=None):
     return a
 
 
+def _oracle(w, seqs):
+    """float64 oracle on the sequences `seqs`, with only their cache blocks brought to the host."""
+    idx = torch.tensor(seqs, device=DEV)
+    lens = w.seq_lens[idx].cpu()
+    need = max(1, int(np.ceil(lens.numpy() / w.block_size).max()))
+    bt = w.block_tables[idx, :need].cpu()
+    uniq, inv = torch.unique(bt.flatten(), return_inverse=True)
+    kc = w.key_cache[uniq.to(DEV).long()].cpu()
+    vc = w.value_cache[uniq.to(DEV).long()].cpu()
+    return O.paged_attention(w.query[idx].cpu(), kc, vc, w.num_kv_heads, w.scale,
+                             inv.view(bt.shape).int(), lens, None, w.kv_cache_dtype,
+                             float(w.k_scale), float(w.v_scale), mode="f64")
+
+
 @pytest.mark.gpu
-def test_noalloc_matches_caller_scratch_on_consecutive_calls():
+def test_noalloc_matches_the_oracle_on_consecutive_calls():
     stream = torch.cuda.current_stream().cuda_stream
-    # two different batches back to back: the second finds the first one's partials
-    # in the shared buffer and must not be affected by them
+    # Different batches back to back: each finds the previous one's partials in the shared
+    # array and must not be affected by them.  Every case keeps its partials in the built-in
+    # array (this entry point uses nothing else): a small bf16 batch (many slots per sequence),
+    # an fp8 one with block size 32, an fp32 one (generic kernel + separate reduce kernel, 4-byte
+    # partials) and a batch of 256 sequences whose partials fill a third of the array.
     cases = [
         W.small(DEV, seed=31, num_seqs=12, num_heads=32, num_kv_heads=8, max_len=2300, num_blocks=2048),
         W.small(DEV, seed=32, num_seqs=9, num_heads=64, num_kv_heads=8, block_size=32, max_len=1700,
                 kv_cache_dtype="fp8", num_blocks=700),
+        W.small(DEV, seed=34, num_seqs=5, num_heads=8, num_kv_heads=2, max_len=1900, dtype=torch.float32,
+                num_blocks=700),
+        W.small(DEV, seed=35, num_seqs=256, num_heads=32, num_kv_heads=8, max_len=2300, num_blocks=40000),
     ]
-    for w in cases:
-        w.query.mul_(8.0)
-        want = torch.empty_like(w.query)
-        scratch = w.scratch()
-        capi.paged_attention_v2(_args(w, want, scratch), stream)
-        got = torch.full_like(w.query, float("nan"))
-        capi.paged_attention_v2_noalloc(_args(w, got), stream)
-        torch.cuda.synchronize()
-        assert capi.device_status() == 0
-        tol = 2e-2 if w.kv_cache_dtype != "auto" else 1e-2
-        torch.testing.assert_close(got.float(), want.float(), atol=tol, rtol=tol)
-        assert torch.isfinite(got.float()).all()
+    for rounds in range(2):
+        for w in cases:
+            if rounds == 0:
+                w.query.mul_(8.0)
+            got = torch.full_like(w.query, float("nan"))
+            capi.paged_attention_v2_noalloc(_args(w, got), stream)
+            torch.cuda.synchronize()
+            assert capi.device_status() == 0
+            assert torch.isfinite(got.float()).all()
+            tol = 2e-2 if w.kv_cache_dtype != "auto" else 1e-2
+            seqs = list(range(w.num_seqs)) if w.num_seqs <= 16 else [0, 1, 100, 254, 255]
+            want = _oracle(w, seqs)
+            torch.testing.assert_close(got[torch.tensor(seqs, device=DEV)].cpu().double(), want,
+                                       atol=tol, rtol=tol)
+            # and, on every sequence, what v2 gives with scratch that the caller owns
+            ref = torch.empty_like(w.query)
+            capi.paged_attention_v2(_args(w, ref, w.scratch()), stream)
+            torch.testing.assert_close(got.float(), ref.float(), atol=tol, rtol=tol)
 
 
 @pytest.mark.gpu

@@ -26,10 +26,34 @@ def _load() -> None:
 
 _load()
 
-# Always-present private namespaces; `torch.ops._C.*` / `torch.ops._C_cache_ops.*`
-# resolve to the same kernels unless another library defined those names first.
+# Always-present private namespaces.
 _ops = torch.ops._C_b200
 _cache_ops = torch.ops._C_b200_cache_ops
+
+
+def claim_reference_names() -> int:
+    """Registers the kernels under the reference's own operator names as well
+    (``torch.ops._C.paged_attention_v1/v2``, ``merge_attn_states``,
+    ``torch.ops._C_cache_ops.reshape_and_cache/_flash``, ``convert_fp8``, ``copy_blocks``,
+    ``swap_blocks``), for code written against ``torch.ops._C`` that runs WITHOUT vLLM's own
+    extension - the reference's kernel tests and benchmarks, for instance.
+
+    Not done at import time on purpose: had this package defined those names first, importing
+    ``vllm._C`` afterwards would fail on the duplicate definitions.  Names that another
+    library has defined already are left to it; beside an installed vLLM use
+    ``vllm_b200.plugin.register()`` instead.  Returns the number of names claimed by this call
+    (0 when called again).
+    """
+    import ctypes
+
+    fn = ctypes.CDLL(str(_SHIM)).b200_claim_reference_names
+    fn.argtypes = [ctypes.c_char_p, ctypes.c_int]
+    fn.restype = ctypes.c_int
+    buf = ctypes.create_string_buffer(1024)
+    n = fn(buf, len(buf))
+    if n < 0:
+        raise RuntimeError("could not register the reference operator names: " + buf.value.decode())
+    return n
 
 
 def paged_attention_v1(

@@ -62,19 +62,51 @@ def expand_to_token_sequences(query_start_loc: torch.Tensor, seq_lens: torch.Ten
 
 
 class B200PagedAttentionMetadataBuilder:
-    """Builds ``B200PagedAttentionMetadata`` from the engine's common metadata
-    (role of ``RocmAttentionMetadataBuilder``, rocm_attn.py:59-150)."""
+    """Builds ``B200PagedAttentionMetadata`` from the engine's per-step
+    ``CommonAttentionMetadata``.  Same constructor and ``build`` signature as the
+    reference's builders (``AttentionMetadataBuilder``,
+    ``vllm/v1/attention/backends/utils.py:245-330``; ``RocmAttentionMetadataBuilder``,
+    ``rocm_attn.py:65-150``), so the engine can construct and call it unchanged.  The
+    arguments are read by attribute only: any object with the fields of
+    ``CommonAttentionMetadata`` (``utils.py:53-95``) does.
+    """
 
-    def __init__(self, block_size: int):
-        self.block_size = block_size
+    # the ops neither allocate nor synchronise, so decode steps may be captured in full graphs
+    # (the reference spells this AttentionCGSupport.ALWAYS; the name is kept as a string so that
+    # this module does not have to import vLLM)
+    _cudagraph_support = "ALWAYS"
+    reorder_batch_threshold = None
 
-    def build(self, *, num_actual_tokens: int, max_query_len: int, query_start_loc: torch.Tensor,
-              max_seq_len: int, seq_lens: torch.Tensor, block_table: torch.Tensor,
-              slot_mapping: torch.Tensor) -> B200PagedAttentionMetadata:
+    def __init__(self, kv_cache_spec, layer_names=None, vllm_config=None, device=None):
+        # `kv_cache_spec` is the engine's AttentionSpec (block_size attribute); a bare block
+        # size is accepted for stand-alone use
+        self.kv_cache_spec = kv_cache_spec
+        self.layer_names = list(layer_names) if layer_names is not None else []
+        self.vllm_config = vllm_config
+        self.device = device
+        self.block_size = int(getattr(kv_cache_spec, "block_size", kv_cache_spec))
+
+    @classmethod
+    def get_cudagraph_support(cls, vllm_config=None, kv_cache_spec=None):
+        return cls._cudagraph_support
+
+    def build(self, common_prefix_len: int, common_attn_metadata,
+              fast_build: bool = False) -> B200PagedAttentionMetadata:
+        if common_prefix_len > 0:
+            raise NotImplementedError("cascade attention is not supported by the paged-attention ops "
+                                      "(use_cascade_attention() returns False)")
+        m = common_attn_metadata
         return B200PagedAttentionMetadata(
-            num_actual_tokens=num_actual_tokens, max_query_len=max_query_len,
-            query_start_loc=query_start_loc, max_seq_len=max_seq_len, seq_lens=seq_lens,
-            block_table=block_table, slot_mapping=slot_mapping)
+            num_actual_tokens=m.num_actual_tokens, max_query_len=m.max_query_len,
+            query_start_loc=m.query_start_loc, max_seq_len=m.max_seq_len, seq_lens=m.seq_lens,
+            block_table=m.block_table_tensor, slot_mapping=m.slot_mapping)
+
+    def build_for_cudagraph_capture(self, common_attn_metadata) -> B200PagedAttentionMetadata:
+        """Metadata for a capture run: real shapes, every sequence one token long so that the
+        captured launch is cheap (rocm_attn.py:84-99 does the same)."""
+        md = self.build(0, common_attn_metadata)
+        md.seq_lens.fill_(1)
+        return md
 
 
 class B200PagedAttentionImpl:

@@ -115,7 +115,8 @@ def paged_attention_v2(args: AttnArgs, stream: int = 0) -> None:
 
 
 def paged_attention_v2_noalloc(args: AttnArgs, stream: int = 0) -> None:
-    """v2 with the library's built-in 32 MiB split-KV scratch (allocates nothing; see b200pa.h)."""
+    """v2 with the split-KV scratch taken from a 32 MiB array built into the library (allocates
+    nothing; limits and sharing rules in b200pa.h)."""
     check(lib().b200pa_paged_attention_v2_noalloc(C.byref(args), C.c_void_p(stream)))
 
 

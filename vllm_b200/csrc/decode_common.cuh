@@ -27,6 +27,7 @@ struct DecodeParams {
   void* tmp_out;      // [S, Hq, P, D] query dtype, normalised partials
   unsigned* sched;    // [0] work ticket, [1] CTAs done (self-resetting)
   unsigned* arrive;   // per (seq, kv head, head group) count of delivered partials, or nullptr
+  unsigned* arrive2;  // [that][groups_max]: counts per group of pieces (two-level merge), or nullptr
   int* status;
   int64_t q_stride;
   int64_t kv_block_stride;
@@ -36,13 +37,15 @@ struct DecodeParams {
   int num_kv_heads;
   int block_size;
   int max_blocks_per_seq;
-  int max_partitions;  // P; 0 = unsplit: one work item covers the whole sequence
-  int part_tokens;     // tokens per partition (512 with caller scratch; 64..512 in the library workspace)
-  int len_cap;         // sequence lengths are clamped to this (max_partitions * part_tokens when split)
+  int max_partitions;  // P: partial slots per (sequence, head) in the scratch; 0 = unsplit
+  int part_tokens;     // generic kernel: tokens per partition (512)
+  int len_cap;         // sequence lengths are clamped to this
   int group;           // query heads per kv head
   int head_groups;     // ceil(group / heads per item)
   int nstages;         // ring slots per warp
-  int use_table;       // 1: per-sequence partition prefix table in shared memory
+  int groups_max;      // ceil(max_partitions / pieces per merge group)
+  int use_table;       // 1: split launch (per-sequence unit prefix table in shared memory)
+  int min_chunk;       // split launch: smallest range worth a work item, in cache blocks (even)
   float scale;
   // block-sparse attention of the reference signature (generic kernel only); enabled when
   // bs_vert_stride > 1 (attention_kernels.cuh:204-251)

@@ -3,13 +3,19 @@
 // (csrc/attention/attention_kernels.cuh:81-491).
 //
 // Design (bandwidth first; the KV cache is read exactly once):
-//   * One persistent CTA per SM.  Every WARP is an independent worker: it owns work
-//     items (sequence, kv head, partition of 64..512 tokens) - dealt out by a fixed
-//     stride when there are few, pulled from a global ticket counter when there are
-//     many - streams an item's KV pages through its own ring of shared-memory slots
-//     and writes the item's result itself.  There is no CTA-wide barrier after
-//     set-up, and a warp keeps prefetching pages of its NEXT item while it
-//     finishes the current one, so the pipeline never drains.
+//   * One persistent CTA per SM.  Every WARP is an independent worker that streams
+//     KV pages through its own ring of shared-memory slots and writes its results
+//     itself.  There is no CTA-wide barrier after set-up, and a warp keeps
+//     prefetching pages of its NEXT work item while it finishes the current one, so
+//     the pipeline never drains.
+//   * Split-KV work is cut by PAGE COUNT, not by sequence: the cache blocks of all
+//     (kv head, sequence) pairs form one flat list, every warp takes one contiguous
+//     range of equal length, and the pieces of a sequence that a range covers are its
+//     work items.  The cut is computed inside the kernel from the real sequence
+//     lengths, so every warp reads the same number of bytes whatever the length
+//     distribution.  Without scratch memory a work item is a whole (sequence, kv
+//     head), dealt out by a fixed stride when there are few and pulled from a global
+//     ticket counter when there are many.
 //   * The warp that delivers the last partial of a sequence merges all of them
 //     (no second launch, nobody waits).
 //   * A KV page (one block of one kv head) is contiguous in both cache layouts:
@@ -78,50 +84,75 @@ __device__ __forceinline__ int load_bt(const DecodeParams& p, const WorkItem& it
   return __ldg(p.block_tables + int64_t(it.seq) * p.max_blocks_per_seq + it.first_page + pg);
 }
 
-// Merges the split-KV partials of `nheads` consecutive heads of one sequence into `outp`
-// (the reference's paged_attention_v2_reduce_kernel, attention_kernels.cuh:559-664, for one
-// warp).  row0 = index of the first head's row in exp_sums / max_logits ([.., P] floats) and,
-// times D, in tmp_out.  Overwrites exp_sums with the normalised weights.  Kept out of line:
-// it runs once per sequence and kv head and must not cost the page loop any registers.
+// Sequences cut into more than kMergeDirectMax pieces are merged in two levels: the pieces form
+// groups of kMergeFan consecutive ones, the warp that completes a group merges it into one
+// partial (kept in the group's first slot), and the warp that completes the last group merges
+// the groups.  One warp merging 60 partials of four heads takes ~14 us, which would be the
+// tail of the launch; groups are merged by different warps as they finish.
+constexpr int kMergeFan = 8;
+constexpr int kMergeDirectMax = 16;
+
+// Merges split-KV partials of `nheads` consecutive heads of one sequence (the reference's
+// paged_attention_v2_reduce_kernel, attention_kernels.cuh:559-664, for one warp).
+// Partial j of head h has its (max logit, exp sum) at index row0 + h*P + j*pstride of
+// max_logits / exp_sums and its normalised output at that index times D in tmp.
+//   group == false: writes out = sum_j w_j O_j with w_j = l_j 2^(m_j-M) / (sum + 1e-6) to
+//     outp + h*out_head_stride, and the log-sum-exp if asked.
+//   group == true (pstride 1, 2 <= np <= 32): the same sum with w_j = l_j 2^(m_j-M) / sum goes
+//     into partial 0's slot of tmp (outp points there) and (M, sum) into its statistics, so that
+//     the slot again holds a partial in the format above.
+// Overwrites exp_sums with the weights.  Kept out of line: it runs once per sequence and kv head
+// and must not cost the page loop any registers.
 template <typename QT, int D>
-__device__ __noinline__ void merge_partials(float* exp_sums, const float* max_logits,
-                                            const QT* tmp, QT* outp, int64_t row0, int np, int P,
-                                            int nheads, int lane, float* lse, int lse_stride) {
+__device__ __noinline__ void merge_partials(float* exp_sums, float* max_logits, const QT* tmp,
+                                            QT* outp, int64_t out_head_stride, int64_t row0, int np,
+                                            int P, int pstride, int nheads, int lane, float* lse,
+                                            int lse_stride, bool group) {
   constexpr bool kOutBf = std::is_same_v<QT, __nv_bfloat16>;
-  // Phase 1: per head, turn (max logit, exp sum) of its partitions into normalised weights.
-  // Lanes run over partitions, four heads share one memory round trip.
+  // Phase 1: per head, turn (max logit, exp sum) of its partials into normalised weights.
+  // Lanes run over partials, four heads share one memory round trip.
   for (int h0 = 0; h0 < nheads; h0 += 4) {
     float ml0[4], es0[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const bool ok = h0 + k < nheads && lane < np;
-      const int64_t at = row0 + int64_t(ok ? h0 + k : h0) * P + (ok ? lane : 0);
+      const int64_t at = row0 + int64_t(ok ? h0 + k : h0) * P + int64_t(ok ? lane : 0) * pstride;
       ml0[k] = ok ? __ldcg(max_logits + at) : -INFINITY;
       es0[k] = ok ? __ldcg(exp_sums + at) : 0.f;
     }
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       if (h0 + k >= nheads) break;  // warp-uniform
-      const float* ml = max_logits + row0 + int64_t(h0 + k) * P;
+      float* ml = max_logits + row0 + int64_t(h0 + k) * P;
       float* es = exp_sums + row0 + int64_t(h0 + k) * P;
       float mx = ml0[k];
-      for (int j = lane + 32; j < np; j += 32) mx = fmaxf(mx, __ldcg(ml + j));
+      for (int j = lane + 32; j < np; j += 32) mx = fmaxf(mx, __ldcg(ml + int64_t(j) * pstride));
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
       const float w0 = lane < np ? es0[k] * fast_exp2(ml0[k] - mx) : 0.f;
       float sum = w0;
       for (int j = lane + 32; j < np; j += 32) {
-        const float w = __ldcg(es + j) * fast_exp2(__ldcg(ml + j) - mx);
-        es[j] = w;
+        const float w = __ldcg(es + int64_t(j) * pstride) * fast_exp2(__ldcg(ml + int64_t(j) * pstride) - mx);
+        es[int64_t(j) * pstride] = w;
         sum += w;
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-      const float winv = __fdividef(1.f, sum + 1e-6f);
-      if (lane < np) es[lane] = w0 * winv;
-      for (int j = lane + 32; j < np; j += 32) es[j] *= winv;
+      const float winv = __fdividef(1.f, group ? sum : sum + 1e-6f);
+      if (lane < np) es[int64_t(lane) * pstride] = w0 * winv;
+      for (int j = lane + 32; j < np; j += 32) es[int64_t(j) * pstride] *= winv;
+      if (group) {
+        // every lane has its max logits in registers (np <= 32): their slots can take the
+        // merged statistics; the exp sum waits in partial 1's slot until the weights are used
+        __syncwarp();
+        if (lane == 0) {
+          ml[0] = mx;
+          ml[1] = sum;
+        }
+      }
       // log-sum-exp of the whole sequence (logits are kept in the log2 domain)
-      if (lse != nullptr && lane == 0) lse[int64_t(h0 + k) * lse_stride] = (mx + log2f(sum)) * kLn2;
+      if (!group && lse != nullptr && lane == 0)
+        lse[int64_t(h0 + k) * lse_stride] = (mx + log2f(sum)) * kLn2;
     }
   }
   __syncwarp();  // weights written by other lanes are read below
@@ -129,6 +160,7 @@ __device__ __noinline__ void merge_partials(float* exp_sums, const float* max_lo
   // (16 bytes) of one head; every load is independent of every other.
   constexpr int UPH = D / 8;  // units per head
   const int units = nheads * UPH;
+  const int64_t jstep = int64_t(pstride) * D;
   auto fma8 = [&](float* acc, float w, const uint4& v) {
     const uint32_t vv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -155,7 +187,7 @@ __device__ __noinline__ void merge_partials(float* exp_sums, const float* max_lo
     *reinterpret_cast<uint4*>(dst) = o4;
   };
   if (units <= 32) {
-    // few units: several lanes share a unit and split its partitions
+    // few units: several lanes share a unit and split its partials
     int u2 = 1;
     while (u2 < units) u2 <<= 1;
     const int lpu = 32 / u2;  // lanes per unit
@@ -172,15 +204,16 @@ __device__ __noinline__ void merge_partials(float* exp_sums, const float* max_lo
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
 #pragma unroll 8
     for (int j = sub; j < np; j += lpu) {
-      const float w = __ldcg(wt + j);
-      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src + int64_t(j) * D));
+      const float w = __ldcg(wt + int64_t(j) * pstride);
+      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src + int64_t(j) * jstep));
       fma8(acc, w, v);
     }
     for (int o = u2; o < 32; o <<= 1) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
     }
-    if (ok && sub == 0) store8(outp + hl * D + e0, acc);
+    __syncwarp();  // (group) partial 0 is a source of other lanes and the destination
+    if (ok && sub == 0) store8(outp + hl * out_head_stride + e0, acc);
   } else {
     // many units: a lane works on two of them at once
     for (int u0 = lane; u0 < units; u0 += 64) {
@@ -201,16 +234,24 @@ __device__ __noinline__ void merge_partials(float* exp_sums, const float* max_lo
       for (int j = 0; j < np; ++j) {
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
-          const float w = __ldcg(wt[k] + j);
-          const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src[k] + int64_t(j) * D));
+          const float w = __ldcg(wt[k] + int64_t(j) * pstride);
+          const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src[k] + int64_t(j) * jstep));
           fma8(acc[k], w, v);
         }
       }
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
         const int u = u0 + 32 * k;
-        if (u < units) store8(outp + (u / UPH) * D + (u % UPH) * 8, acc[k]);
+        if (u < units) store8(outp + (u / UPH) * out_head_stride + (u % UPH) * 8, acc[k]);
       }
+    }
+  }
+  if (group) {
+    // the merged partial's exp sum moves to its place (the weights have been used)
+    __syncwarp();
+    if (lane < nheads) {
+      const int64_t at = row0 + int64_t(lane) * P;
+      exp_sums[at] = max_logits[at + 1];
     }
   }
 }
@@ -245,9 +286,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
   // and one barrier (half the barrier traffic).  The host uses the same rule.
   constexpr bool split_kv = step_bytes >= 4096;
   constexpr uint32_t slot_bytes = split_kv ? step_bytes : 2 * step_bytes;
-  const int PT = p.part_tokens;  // tokens per split-KV partition (a multiple of the block size)
-
-  // ---- shared memory carve-up: [partition prefix table][mbarriers][stages]
+  // ---- shared memory carve-up: [unit prefix table][mbarriers][stages]
   int* cum = reinterpret_cast<int*>(smem_raw);
   const int table_ints = p.use_table ? ((p.num_seqs + 1 + 3) & ~3) : 0;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + size_t(table_ints) * 4);
@@ -255,49 +294,90 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
   unsigned char* slots = smem_raw + size_t(table_ints) * 4 + bars_bytes;
   // the dynamic buffer is 128-byte aligned and table_ints*4 is a multiple of 16
 
-  // ---- set-up: prefix table of partitions per sequence (exclusive scan)
-  if (p.use_table) {
+  // ---- set-up of a split launch: the flat list of work units.
+  // A unit is one cache block of one (kv head, head group, sequence); a sequence counts
+  // max(2, blocks rounded up to even) units, so that every sequence start - and with an even
+  // range length every cut - falls on an even block and an empty sequence still has a unit
+  // that gets its (zero) output written.  The list is ordered (head, sequence, block); warp r
+  // of the grid takes units [r*C, (r+1)*C).
+  __shared__ int s_plan[4];      // [0] C: units per range, [1] units of one head, [2] ranges
+  __shared__ int4 s_iter[MAXW];  // per warp: units left, block offset, sequence, head
+  const bool flat = p.use_table != 0;
+  const int hsubs = p.num_kv_heads * p.head_groups;
+  if (flat) {
     __shared__ int warp_tot[MAXW];
+    __shared__ int warp_mx[MAXW];
     const int S = p.num_seqs;
     const int per = (S + blockDim.x - 1) / blockDim.x;
     const int s0 = min(S, int(threadIdx.x) * per);
     const int s1 = min(S, s0 + per);
-    int mine = 0;
+    auto units_of = [&](int s) {
+      const int len = min(max(p.seq_lens[s], 0), p.len_cap);
+      return max(2, ((len + B - 1) / B + 1) & ~1);
+    };
+    int mine = 0, mx = 0;
     for (int s = s0; s < s1; ++s) {
-      const int len = min(p.seq_lens[s], p.len_cap);
-      mine += max(1, (len + PT - 1) / PT);
+      const int n = units_of(s);
+      mine += n;
+      mx = max(mx, n);
     }
     int incl = mine;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const int v = __shfl_up_sync(0xffffffffu, incl, o);
       if (lane >= o) incl += v;
+      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     }
-    if (lane == 31) warp_tot[warp] = incl;
+    if (lane == 31) {
+      warp_tot[warp] = incl;
+      warp_mx[warp] = mx;
+    }
     __syncthreads();
     int base = 0;
     for (int w = 0; w < warp; ++w) base += warp_tot[w];
     int run = base + incl - mine;
     for (int s = s0; s < s1; ++s) {
       cum[s] = run;
-      const int len = min(p.seq_lens[s], p.len_cap);
-      run += max(1, (len + PT - 1) / PT);
+      run += units_of(s);
     }
     if (threadIdx.x == blockDim.x - 1) cum[S] = run;
+    if (threadIdx.x == 0) {
+      int total = 0, n_max = 2;
+      for (int w = 0; w < nwarps; ++w) {
+        total += warp_tot[w];
+        n_max = max(n_max, warp_mx[w]);
+      }
+      // Range length: an equal share for every warp of the grid, at least the smallest range
+      // worth a work item, and large enough that the longest sequence is cut into no more
+      // pieces than the scratch has slots per sequence (a sequence of n units meets at most
+      // (n - 1) / C + 2 ranges).  Even, see above.
+      const long long U = (long long)hsubs * total;
+      const long long W = (long long)gridDim.x * nwarps;
+      long long C = (U + W - 1) / W;
+      C = max(C, (long long)p.min_chunk);
+      C = max(C, (long long)((n_max - 1) / max(1, p.max_partitions - 1) + 1));
+      C = (C + 1) & ~1ll;
+      s_plan[0] = int(min(C, (long long)INT32_MAX - 1));
+      s_plan[1] = total;
+      s_plan[2] = int((U + C - 1) / C);
+    }
   }
   __syncthreads();
 
-  const int hsubs = p.num_kv_heads * p.head_groups;
-  const int total_parts = p.use_table ? cum[p.num_seqs] : p.num_seqs;
-  const unsigned total_items = unsigned(total_parts) * unsigned(hsubs);
+  const unsigned grid_warps = gridDim.x * unsigned(nwarps);
+  // work items of an unsplit launch / ranges of a split one
+  const unsigned total_items = flat ? unsigned(s_plan[2]) : unsigned(p.num_seqs) * unsigned(hsubs);
+  // Ranges and the first items are numbered SM-first: warp w of CTA b has number
+  // w * gridDim.x + b, so a launch with fewer of them than warps leaves the
+  // highest-numbered warps of every CTA idle.
+  const unsigned my_number = unsigned(warp) * gridDim.x + blockIdx.x;
 
-  // Ring of this warp.  The host sizes warps and slots from max_seq_len, the only length it
-  // knows; when the batch turns out to have fewer items than the grid has warps, the warps
-  // without an item (the highest-numbered ones of each CTA, see the item numbering below)
-  // leave their slots and barriers to the others: fewer busy warps, each with more pages in
-  // flight, which is what a launch bound by the latency of one item needs.
+  // Ring of this warp.  The host sizes warps and slots without knowing the lengths; when the
+  // batch turns out to have fewer ranges / items than the grid has warps, the warps without
+  // one leave their slots and barriers to the others: fewer busy warps, each with more pages
+  // in flight, which is what a launch bound by the latency of one item needs.
   int NSLOT = slots_per_warp;
-  if (total_items < gridDim.x * unsigned(nwarps)) {
+  if (total_items < grid_warps) {
     const int busy = max(1, int((total_items + gridDim.x - 1) / gridDim.x));  // per CTA, at most
     NSLOT = min(8, nwarps * slots_per_warp / busy);
   }
@@ -310,18 +390,41 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
     for (int s = 0; s < NSLOT; ++s) mbar_init(my_bar0 + s * 8, 1);
     fence_barrier_init();
   }
+  // where range r starts: head, sequence (binary search), block offset
+  auto start_range = [&](unsigned r) -> int4 {
+    int4 st = make_int4(0, 0, 0, 0);
+    if (r < total_items) {
+      const int C = s_plan[0], TP = s_plan[1];
+      const long long U = (long long)hsubs * TP;
+      const long long u0 = (long long)r * C;
+      st.x = int(min((long long)C, U - u0));
+      st.w = int(u0 / TP);
+      const int rem = int(u0 - (long long)st.w * TP);
+      int lo = 0, hi = p.num_seqs;  // cum[lo] <= rem < cum[hi]
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (cum[mid] <= rem) lo = mid; else hi = mid;
+      }
+      st.z = lo;
+      st.y = rem - cum[lo];
+    }
+    return st;
+  };
+  if (flat) {
+    const int4 st = start_range(my_number);
+    if (lane == 0) s_iter[warp] = st;
+  }
   __syncwarp();
   const uint64_t policy = policy_evict_first();
   const char* kc_base = static_cast<const char*>(p.kc);
   const char* vc_base = static_cast<const char*>(p.vc);
 
-  // Up to three items per resident warp: warp w of the grid owns items w, w + W, w + 2W
-  // (W = warps in the grid; numbered so that consecutive items land on different SMs).  No
-  // ticket round trips, and nobody holds a second item while another warp idles.  Larger
-  // launches pull tickets from the global counter, which balances items of unequal length.
-  const unsigned grid_warps = gridDim.x * unsigned(nwarps);
-  const bool strided = total_items <= 3u * grid_warps;
-  unsigned next_strided = unsigned(warp) * gridDim.x + blockIdx.x;
+  // Unsplit launches: up to three items per resident warp are dealt out by a fixed stride
+  // (warp number, + W, + 2W; W = warps in the grid): no ticket round trips, and nobody holds a
+  // second item while another warp idles.  Larger launches pull tickets from the global
+  // counter, which balances items of unequal length.
+  const bool strided = !flat && total_items <= 3u * grid_warps;
+  unsigned next_strided = my_number;
 
   auto fetch = [&]() -> unsigned {
     if (strided) {
@@ -334,62 +437,100 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
     return __shfl_sync(0xffffffffu, v, 0);
   };
 
-  auto decode = [&](unsigned raw) -> WorkItem {
+  auto blank_item = [&]() -> WorkItem {
     WorkItem it;
-    it.valid = raw < total_items;
+    it.valid = false;
     it.seq = it.kvh = it.hg = it.part = it.tok_begin = it.tok_end = it.first_page = it.npages = 0;
     it.nparts = 1;
     it.win = 0;
     it.bt = 0;
+    return it;
+  };
+
+  // unsplit: item number -> (sequence, head), the whole sequence
+  auto decode = [&](unsigned raw) -> WorkItem {
+    WorkItem it = blank_item();
+    it.valid = raw < total_items;
     if (!it.valid) return it;
     const int hsub = int(raw % unsigned(hsubs));
-    const int cg = int(raw / unsigned(hsubs));
+    it.seq = int(raw / unsigned(hsubs));
     it.kvh = hsub / p.head_groups;
     it.hg = hsub % p.head_groups;
-    if (p.use_table) {
-      int lo = 0, hi = p.num_seqs;  // cum[lo] <= cg < cum[hi]
-      while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (cum[mid] <= cg) lo = mid; else hi = mid;
-      }
-      it.seq = lo;
-      it.part = cg - cum[lo];
-      it.nparts = cum[lo + 1] - cum[lo];
-      it.tok_begin = it.part * PT;
-      it.tok_end = min(min(p.seq_lens[lo], p.len_cap), it.tok_begin + PT);
-    } else {
-      it.seq = cg;
-      it.tok_begin = 0;
-      it.tok_end = p.seq_lens[cg];
-    }
-    if (it.tok_end < it.tok_begin) it.tok_end = it.tok_begin;
-    it.first_page = it.tok_begin / B;
-    it.npages = (it.tok_end - it.tok_begin + B - 1) / B;
+    it.tok_end = max(p.seq_lens[it.seq], 0);
+    it.npages = (it.tok_end + B - 1) / B;
     it.bt = load_bt(p, it, 0, lane);
     return it;
   };
 
-  // A warp always knows its current item, the next one (decoded, block ids loaded) and the
-  // number of the one after.  With tickets, the second and third are requested as soon as the
-  // first has arrived and their round trips overlap with the decoding of the first.
-  const unsigned raw0 = fetch();
-  unsigned raw1 = 0, raw2 = 0;
-  if (strided) {
-    raw1 = fetch();
-    raw2 = fetch();
-  } else if (lane == 0) {
-    raw1 = atomicAdd(p.sched, 1u);
-    raw2 = atomicAdd(p.sched, 1u);
+  // split: the next piece of this warp's range.  The iterator lives in shared memory so that
+  // the page loop carries no registers for it.
+  auto next_piece = [&]() -> WorkItem {
+    WorkItem it = blank_item();
+    int4 st = s_iter[warp];
+    it.valid = st.x > 0;
+    if (!it.valid) return it;
+    const int C = s_plan[0], TP = s_plan[1];
+    const int c0 = cum[st.z];
+    const int n = cum[st.z + 1] - c0;      // units of this sequence
+    const int take = min(n - st.y, st.x);  // units of it that fall into the range
+    const int len = min(max(p.seq_lens[st.z], 0), p.len_cap);
+    it.seq = st.z;
+    it.kvh = st.w / p.head_groups;
+    it.hg = st.w % p.head_groups;
+    // the ranges that meet this (head, sequence) are consecutive; each delivers one partial
+    const long long base = (long long)st.w * TP + c0;
+    const int w_lo = int(base / C);
+    it.nparts = int((base + n - 1) / C) - w_lo + 1;
+    it.part = int((base + st.y) / C) - w_lo;
+    it.first_page = st.y;
+    it.tok_begin = st.y * B;
+    it.tok_end = max(it.tok_begin, min(len, (st.y + take) * B));
+    it.npages = (it.tok_end - it.tok_begin + B - 1) / B;
+    it.bt = load_bt(p, it, 0, lane);
+    st.x -= take;
+    st.y += take;
+    if (st.y == n) {
+      st.y = 0;
+      if (++st.z == p.num_seqs) {
+        st.z = 0;
+        ++st.w;
+      }
+    }
+    __syncwarp();
+    if (lane == 0) s_iter[warp] = st;
+    __syncwarp();
+    return it;
+  };
+
+  // A warp always knows its current item and the next one (decoded, block ids loaded); an
+  // unsplit launch also the number of the one after.  With tickets, the second and third are
+  // requested as soon as the first has arrived and their round trips overlap with the
+  // decoding of the first.
+  WorkItem cur, nxt;
+  unsigned nn_raw = 0;
+  if (flat) {
+    cur = next_piece();
+    nxt = next_piece();
+  } else {
+    const unsigned raw0 = fetch();
+    unsigned raw1 = 0, raw2 = 0;
+    if (strided) {
+      raw1 = fetch();
+      raw2 = fetch();
+    } else if (lane == 0) {
+      raw1 = atomicAdd(p.sched, 1u);
+      raw2 = atomicAdd(p.sched, 1u);
+    }
+    cur = decode(raw0);
+    if (!strided) {
+      raw1 = __shfl_sync(0xffffffffu, raw1, 0);
+      raw2 = __shfl_sync(0xffffffffu, raw2, 0);
+    }
+    nxt = decode(raw1);
+    nn_raw = raw2;
   }
-  WorkItem cur = decode(raw0);
-  if (!strided) {
-    raw1 = __shfl_sync(0xffffffffu, raw1, 0);
-    raw2 = __shfl_sync(0xffffffffu, raw2, 0);
-  }
-  WorkItem nxt = decode(raw1);
-  unsigned nn_raw = raw2;
   if (!has_ring && cur.valid) {
-    // cannot happen with the item numbering above; never touch slots that are not this warp's
+    // cannot happen with the numbering above; never touch slots that are not this warp's
     if (lane == 0) atomicExch(p.status, kStatusNoRing);
     cur.valid = false;
   }
@@ -828,26 +969,60 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
     if (!direct && p.arrive != nullptr) {
       __threadfence();  // partials visible before the arrival is counted
       __syncwarp();
-      unsigned* cnt = p.arrive + (size_t(cur.seq) * p.num_kv_heads + cur.kvh) * p.head_groups + cur.hg;
-      unsigned old = 0;
-      if (lane == 0) old = atomicAdd(cnt, 1u);
-      old = __shfl_sync(0xffffffffu, old, 0);
-      if (old == unsigned(cur.nparts - 1)) {
-        if (lane == 0) *cnt = 0;  // re-arm for the next launch
-        __threadfence();          // order the loads below after the observed arrivals
-        merge_partials<QT, D>(p.exp_sums, p.max_logits, static_cast<const QT*>(p.tmp_out),
-                              static_cast<QT*>(p.out) + (int64_t(cur.seq) * p.num_heads + hq0) * D,
-                              (int64_t(cur.seq) * p.num_heads + hq0) * p.max_partitions,
-                              cur.nparts, p.max_partitions, nheads, lane,
-                              p.lse ? p.lse + int64_t(hq0) * p.num_seqs + cur.seq : nullptr,
-                              p.num_seqs);
+      const size_t unit = (size_t(cur.seq) * p.num_kv_heads + cur.kvh) * p.head_groups + cur.hg;
+      const int64_t rowbase = (int64_t(cur.seq) * p.num_heads + hq0) * p.max_partitions;
+      QT* tmp_q = static_cast<QT*>(p.tmp_out);
+      int np_top = cur.nparts, stride_top = 1;
+      bool go_top = true;
+      if (p.arrive2 != nullptr && cur.nparts > kMergeDirectMax) {
+        // two levels: this piece's group first
+        const int gidx = cur.part / kMergeFan;
+        const int gsize = min(kMergeFan, cur.nparts - gidx * kMergeFan);
+        np_top = (cur.nparts + kMergeFan - 1) / kMergeFan;
+        stride_top = kMergeFan;
+        if (gsize > 1) {
+          unsigned* cnt2 = p.arrive2 + unit * p.groups_max + gidx;
+          unsigned old2 = 0;
+          if (lane == 0) old2 = atomicAdd(cnt2, 1u);
+          old2 = __shfl_sync(0xffffffffu, old2, 0);
+          go_top = old2 == unsigned(gsize - 1);
+          if (go_top) {
+            if (lane == 0) *cnt2 = 0;  // re-arm for the next launch
+            __threadfence();           // order the loads below after the observed arrivals
+            const int64_t g0 = rowbase + gidx * kMergeFan;
+            merge_partials<QT, D>(p.exp_sums, p.max_logits, tmp_q, tmp_q + g0 * D,
+                                  int64_t(p.max_partitions) * D, g0, gsize, p.max_partitions, 1,
+                                  nheads, lane, nullptr, 0, true);
+            __threadfence();
+            __syncwarp();
+          }
+        }
+      }
+      if (go_top) {
+        unsigned* cnt = p.arrive + unit;
+        unsigned old = 0;
+        if (lane == 0) old = atomicAdd(cnt, 1u);
+        old = __shfl_sync(0xffffffffu, old, 0);
+        if (old == unsigned(np_top - 1)) {
+          if (lane == 0) *cnt = 0;  // re-arm for the next launch
+          __threadfence();          // order the loads below after the observed arrivals
+          merge_partials<QT, D>(p.exp_sums, p.max_logits, tmp_q,
+                                static_cast<QT*>(p.out) + (int64_t(cur.seq) * p.num_heads + hq0) * D, D,
+                                rowbase, np_top, p.max_partitions, stride_top, nheads, lane,
+                                p.lse ? p.lse + int64_t(hq0) * p.num_seqs + cur.seq : nullptr,
+                                p.num_seqs, false);
+        }
       }
     }
 
     // ---- advance to the next item
     cur = nxt;
-    nxt = decode(nn_raw);
-    nn_raw = fetch();
+    if (flat) {
+      nxt = next_piece();
+    } else {
+      nxt = decode(nn_raw);
+      nn_raw = fetch();
+    }
     // the producer either already works on the new `cur` (keep its state) or starts it now
     if (prod_sel == 1) prod_sel = 0; else producer_take(cur);
     while (inflight < NSLOT && produce_one()) {}

@@ -10,6 +10,7 @@
 #include <cstdint>
 #include <cstdlib>
 #include <iterator>
+#include <mutex>
 
 #include "decode_inst.cuh"
 
@@ -210,60 +211,145 @@ pa_generic_kernel(const DecodeParams p, int head_size, int x) {
 __device__ unsigned g_sched_words[256][2];  // zero-initialised; self-resetting per launch
 // Arrival counters of the fused split-KV merge: one per (sequence, kv head, head
 // group); zero-initialised and re-armed by the warp that performs the merge.
-constexpr int kArriveRegions = 8;
-constexpr int kArrivePerRegion = 16384;
-__device__ unsigned g_arrive[kArriveRegions][kArrivePerRegion];
+constexpr int kStreamSlots = 8;
+constexpr int kArrivePerRegion = 32768;
+__device__ unsigned g_arrive[kStreamSlots][kArrivePerRegion];
+// ... and one per group of pieces of a sequence that is merged in two levels
+constexpr int kArrive2PerRegion = 65536;
+__device__ unsigned g_arrive2[kStreamSlots][kArrive2PerRegion];
 
 // Split-KV workspace of the library.  The reference's v1 has no scratch argument, so a
 // sequence could only be handled by one work item; with a small batch that leaves most of
-// the GPU idle.  v1 therefore splits sequences into partitions of 64..512 tokens when the
-// partials fit this buffer, exactly like v2 does with the caller's scratch; v2 switches to
-// it as well when the caller's 512-token partitions are too coarse to fill the GPU.
-// Shared by all such calls on a device (one stream at a time).
-constexpr size_t kV1ScratchBytes = size_t(32) << 20;
-static __device__ __align__(256) unsigned char g_v1_scratch[kV1ScratchBytes];
+// the GPU idle.  v1 therefore splits sequences across warps through this buffer exactly
+// like v2 does through the caller's scratch, and v2 switches to it when the caller's
+// scratch has too few partition slots per sequence for the batch (few, long sequences).
+//
+// Calls on different streams may overlap on the GPU, so every stream gets a region of its
+// own (and its own arrival counters): the first stream seen on a device - the one stream of
+// a typical engine - the large region, up to seven more a small one each.  Calls on one
+// stream are ordered by the stream and share its region.
+constexpr size_t kBigRegionBytes = size_t(32) << 20;
+constexpr size_t kSmallRegionBytes = size_t(4) << 20;
+constexpr size_t kWorkspaceBytes = kBigRegionBytes + (kStreamSlots - 1) * kSmallRegionBytes;
+static __device__ __align__(256) unsigned char g_workspace[kWorkspaceBytes];
 
-static unsigned char* v1_scratch_ptr() {
+struct StreamRegion {
+  unsigned char* ws;   // split-KV workspace of this stream
+  size_t ws_bytes;
+  unsigned* arrive;    // arrival counters of this stream
+  unsigned* arrive2;   // ... of its merge groups
+};
+
+// Developer knobs, read from the environment once per process (B200PA_TUNE_RELOAD=1 at
+// that first read makes every call read them again, for parameter sweeps in one process).
+struct Tuning {
+  int no_split = 0;      // B200PA_TUNE_NO_SPLIT=1: never use the library workspace
+  int max_parts = 0;     // B200PA_TUNE_MAX_PARTS: cap on partial slots per sequence (>= 2)
+  int min_tokens = 0;    // B200PA_TUNE_MIN_TOKENS: smallest range, in tokens (multiple of 32)
+  int warps = 0;         // B200PA_TUNE_WARPS: warps per CTA
+  int stages = 0;        // B200PA_TUNE_STAGES: ring slots per warp
+  int reload = 0;
+};
+
+static int env_int(const char* name, int lo, int hi) {
+  const char* e = getenv(name);
+  if (e == nullptr || *e == 0) return 0;
+  const long v = strtol(e, nullptr, 10);
+  return (v < lo || v > hi) ? 0 : int(v);  // out of range: ignored
+}
+
+static Tuning read_tuning() {
+  Tuning t;
+  t.no_split = env_int("B200PA_TUNE_NO_SPLIT", 0, 1);
+  t.max_parts = env_int("B200PA_TUNE_MAX_PARTS", 2, 1024);
+  t.min_tokens = env_int("B200PA_TUNE_MIN_TOKENS", 32, 1 << 20) & ~31;
+  t.warps = env_int("B200PA_TUNE_WARPS", 1, 16);
+  t.stages = env_int("B200PA_TUNE_STAGES", 1, 8);
+  t.reload = env_int("B200PA_TUNE_RELOAD", 0, 1);
+  return t;
+}
+
+static Tuning tuning() {
+  static const Tuning first = read_tuning();
+  return first.reload ? read_tuning() : first;
+}
+
+// Region of the calling stream on the current device, or false when the device's eight
+// stream slots are taken by other streams (the caller then runs without the library's
+// scratch and counters).  A slot whose stream has not been used for the longest time is
+// handed to a new stream, so streams that have been destroyed do not use the slots up;
+// more than eight streams calling concurrently are not kept apart.
+static bool stream_region(cudaStream_t stream, StreamRegion* out) {
   constexpr int kMaxDev = 64;
-  static unsigned char* cache[kMaxDev] = {};
+  struct DevState {
+    unsigned char* ws = nullptr;
+    unsigned* arrive = nullptr;
+    unsigned* arrive2 = nullptr;
+    uintptr_t key[kStreamSlots] = {};
+    uint64_t used[kStreamSlots] = {};
+    int n = 0;
+    uint64_t clock = 0;
+  };
+  static DevState state[kMaxDev];
+  static std::mutex mu;
+  static thread_local char thread_tag;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return false;
+  // the legacy default stream has two handles; the per-thread default stream is one handle
+  // for a different stream in every host thread
+  uintptr_t key = reinterpret_cast<uintptr_t>(stream);
+  if (stream == cudaStreamLegacy) key = 0;
+  if (stream == cudaStreamPerThread) key = reinterpret_cast<uintptr_t>(&thread_tag) | 1u;
+  key += 16;  // 0 marks a free entry
+  std::lock_guard<std::mutex> lock(mu);
+  DevState& d = state[dev];
+  if (d.ws == nullptr) {
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&d.ws), g_workspace) != cudaSuccess ||
+        cudaGetSymbolAddress(reinterpret_cast<void**>(&d.arrive), g_arrive) != cudaSuccess ||
+        cudaGetSymbolAddress(reinterpret_cast<void**>(&d.arrive2), g_arrive2) != cudaSuccess) {
+      (void)cudaGetLastError();
+      d.ws = nullptr;
+      return false;
+    }
+  }
+  int idx = -1;
+  for (int i = 0; i < d.n; ++i)
+    if (d.key[i] == key) idx = i;
+  if (idx < 0) {
+    if (d.n < kStreamSlots) {
+      idx = d.n++;
+    } else {
+      idx = 1;  // the large region stays with the first stream
+      for (int i = 2; i < kStreamSlots; ++i)
+        if (d.used[i] < d.used[idx]) idx = i;
+    }
+    d.key[idx] = key;
+  }
+  d.used[idx] = ++d.clock;
+  out->ws = idx == 0 ? d.ws : d.ws + kBigRegionBytes + size_t(idx - 1) * kSmallRegionBytes;
+  out->ws_bytes = idx == 0 ? kBigRegionBytes : kSmallRegionBytes;
+  out->arrive = d.arrive + size_t(idx) * kArrivePerRegion;
+  out->arrive2 = d.arrive2 + size_t(idx) * kArrive2PerRegion;
+  return true;
+}
+
+// Scheduler words of one launch (256 rotating slots; only unsplit launches with more than
+// three items per warp use them).
+static unsigned* sched_words() {
+  constexpr int kMaxDev = 64;
+  static unsigned* sbase[kMaxDev] = {};
+  static std::atomic<unsigned> rr{0};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return nullptr;
-  unsigned char* ptr = __atomic_load_n(&cache[dev], __ATOMIC_ACQUIRE);
-  if (ptr == nullptr) {
-    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_v1_scratch) != cudaSuccess) {
+  unsigned* sb = __atomic_load_n(&sbase[dev], __ATOMIC_ACQUIRE);
+  if (sb == nullptr) {
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&sb), g_sched_words) != cudaSuccess) {
       (void)cudaGetLastError();
       return nullptr;
     }
-    __atomic_store_n(&cache[dev], ptr, __ATOMIC_RELEASE);
-  }
-  return ptr;
-}
-
-// Picks the scheduler words (256 rotating slots) and the arrival-counter region
-// (8 rotating regions) of one launch.  Rotation keeps launches that overlap on
-// different streams apart; launches on one stream are ordered anyway.
-static bool launch_slots(unsigned** sched, unsigned** arrive) {
-  constexpr int kMaxDev = 64;
-  static unsigned* sbase[kMaxDev] = {};
-  static unsigned* abase[kMaxDev] = {};
-  static std::atomic<unsigned> rr{0};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return false;
-  unsigned* sb = __atomic_load_n(&sbase[dev], __ATOMIC_ACQUIRE);
-  unsigned* ab = __atomic_load_n(&abase[dev], __ATOMIC_ACQUIRE);
-  if (sb == nullptr || ab == nullptr) {
-    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&sb), g_sched_words) != cudaSuccess ||
-        cudaGetSymbolAddress(reinterpret_cast<void**>(&ab), g_arrive) != cudaSuccess) {
-      (void)cudaGetLastError();
-      return false;
-    }
-    __atomic_store_n(&abase[dev], ab, __ATOMIC_RELEASE);
     __atomic_store_n(&sbase[dev], sb, __ATOMIC_RELEASE);
   }
-  const unsigned slot = rr.fetch_add(1, std::memory_order_relaxed);
-  *sched = sb + 2 * (slot & 255u);
-  *arrive = ab + size_t(slot % kArriveRegions) * kArrivePerRegion;
-  return true;
+  return sb + 2 * (rr.fetch_add(1, std::memory_order_relaxed) & 255u);
 }
 
 static int sm_count() {
@@ -344,7 +430,17 @@ static bool force_generic() {
   return v == 1;
 }
 
-static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
+// How an attention call may use scratch memory.
+enum class Scratch {
+  kNone,      // paged_attention_v1: no scratch argument; the library workspace if it helps
+  kCaller,    // paged_attention_v2: the caller's exp_sums / max_logits / tmp_out, one partial
+              // slot per 512 tokens of max_seq_len; the library workspace if that is too coarse
+  kOwnArray   // the scratch pointers are an array of the library with `max_num_partitions`
+              // slots per (sequence, head), not tied to 512 tokens; nothing else is used
+};
+
+static int attention_entry(const b200pa_attn_args* a, void* stream, Scratch mode) {
+  const bool v2 = mode != Scratch::kNone;
   B200PA_CHECK_ARG(a != nullptr, "args is NULL");
   B200PA_CHECK_ARG(a->num_seqs >= 0 && a->num_heads > 0 && a->num_kv_heads > 0 && a->head_size > 0,
                    "bad sizes: num_seqs=%d num_heads=%d num_kv_heads=%d head_size=%d", a->num_seqs,
@@ -380,6 +476,17 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
     set_error("Unsupported data type of kv cache: %d", a->kv_dtype);
     return B200PA_EUNSUPPORTED;
   }
+  // The K cache keeps x = 16 / sizeof(cache element) consecutive head dimensions together,
+  // so the head size has to be a multiple of x: an fp8 cache (x = 16) cannot hold head size
+  // 120 (the reference's cache factory asserts the same, vllm/utils/torch_utils.py:259-262).
+  {
+    const int x = a->kv_dtype != B200PA_KV_AUTO ? 16 : 16 / dtype_size(a->q_dtype);
+    if (a->head_size % x != 0) {
+      set_error("Unsupported head size %d for this kv cache type: it is not a multiple of x = %d",
+                a->head_size, x);
+      return B200PA_EUNSUPPORTED;
+    }
+  }
   if (a->num_seqs == 0) return B200PA_OK;
   B200PA_CHECK_ARG(a->out && a->query && a->key_cache && a->value_cache && a->block_tables &&
                        a->seq_lens,
@@ -389,12 +496,14 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
   B200PA_CHECK_ARG(a->max_num_blocks_per_seq > 0, "max_num_blocks_per_seq must be positive");
   if (v2) {
     B200PA_CHECK_ARG(a->exp_sums && a->max_logits && a->tmp_out, "v2 needs exp_sums/max_logits/tmp_out");
-    B200PA_CHECK_ARG(a->max_num_partitions >= 1 &&
+    B200PA_CHECK_ARG(a->max_num_partitions >= 1, "max_num_partitions=%d", a->max_num_partitions);
+    B200PA_CHECK_ARG(mode == Scratch::kOwnArray ||
                          int64_t(a->max_num_partitions) * kPartitionTokens >= a->max_seq_len,
                      "max_num_partitions=%d does not cover max_seq_len=%d", a->max_num_partitions,
                      a->max_seq_len);
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const Tuning tune = tuning();
 
   DecodeParams p{};
   p.out = a->out;
@@ -421,6 +530,7 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
   bool split = v2 && a->max_num_partitions > 1;
   p.max_partitions = split ? a->max_num_partitions : 0;
   p.part_tokens = kPartitionTokens;
+  p.len_cap = INT32_MAX;
   p.group = a->num_heads / a->num_kv_heads;
   p.scale = a->scale;
   p.tp_rank = a->tp_rank;
@@ -459,9 +569,10 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
     const int split_kv = step_bytes >= 4096 ? 1 : 0;           // same rule as in the kernel
     const size_t slot_bytes = split_kv ? step_bytes : 2 * step_bytes;
     const size_t min_slots = split_kv ? 2 : 1;
-    const size_t budget_total = 227 * 1024 - 1024;  // static smem + slack
+    const size_t budget_total = 227 * 1024 - 2048;  // static smem + slack
+    const size_t table_full = size_t((p.num_seqs + 1 + 3) & ~3) * 4;
     auto ring_budget = [&](bool with_table) {
-      const size_t table = with_table ? size_t((p.num_seqs + 1 + 3) & ~3) * 4 : 0;
+      const size_t table = with_table ? table_full : 0;
       return budget_total - std::min(budget_total - 2048, table) - 1024 /* mbarriers */;
     };
     auto warps_for = [&](size_t budget) {
@@ -470,132 +581,108 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
       if (w >= 8) w &= ~3;            // same number of warps on each of the 4 schedulers
       return std::max(w, 1);
     };
-    // The partition prefix table lives in shared memory; very large batches run
-    // without it (one work item per sequence and kv head).
-    if (a->max_seq_len > 64 && p.num_seqs <= 12000 && !getenv("B200PA_TUNE_NO_V1_SPLIT")) {
-      // Split-KV into the library's own workspace when the caller gave no scratch (v1, or v2
-      // with a single 512-token partition) or when the caller's 512-token partitions are too
-      // coarse for the batch.  Two regimes, measured on B200:
-      //  - fewer work items than resident warps: the launch lasts as long as one item, so take
-      //    the finest partition that still gives every item its own warp;
-      //  - more: warps pull several items each and a few items per warp balance the load, so
-      //    refine while there are at most ~4 per warp.
-      // Either way the partitions of one (sequence, kv head) are merged by a single warp,
-      // which bounds how many are worth having (fewer when an item carries many heads).
-      const int64_t warps_total = int64_t(sm_count()) * warps_for(ring_budget(true));
-      const int64_t units = int64_t(p.num_seqs) * p.num_kv_heads * p.head_groups;
-      const int heads_per_item = std::min(p.group, 8 * gp);
-      int max_parts = std::max(16, 64 / heads_per_item);
-      if (const char* e = getenv("B200PA_TUNE_MAX_PARTS")) max_parts = atoi(e);
-      auto parts_of = [&](int t) { return (int64_t(a->max_seq_len) + t - 1) / t; };
-      int pt = kPartitionTokens;
-      const int64_t per_warp = units * parts_of(pt) <= warps_total ? 1 : 4;
-      while (pt > 64 && parts_of(pt / 2) <= max_parts &&
-             units * parts_of(pt / 2) <= per_warp * warps_total)
-        pt /= 2;
-      // fp8 caches: a warp's time goes into its own instruction chain (every cache byte is
-      // converted before the MMA), not into waiting for HBM, so the fixed cost of an item
-      // (~7 us of round trips that nothing overlaps) counts.  Measured on B200 with sequences
-      // of equal length, about 1.7 items per warp is the optimum (config 3: 0.376 ms with
-      // 512-token partitions, 0.345 ms with 2048); with mixed lengths the count estimated from
-      // max_seq_len is about twice the real one and that point is already too coarse.  So:
-      // coarsen while the estimate keeps at least `kMinItemsPerWarp` items per warp, and never
-      // beyond 2048 tokens (larger items of unequal length lengthen the tail of big batches).
-      // 16-bit caches stay at 512 (config 2 loses 5 % with 1024).
-      if (es == 1 && pt == kPartitionTokens) {
-        int min_items_per_warp = 3;
-        if (const char* e = getenv("B200PA_TUNE_FP8_ITEMS")) min_items_per_warp = atoi(e);
-        while (pt < 2048 && parts_of(pt) > 1 &&
-               units * parts_of(2 * pt) >= min_items_per_warp * warps_total)
-          pt *= 2;
-      }
-      if (const char* e = getenv("B200PA_TUNE_PT")) pt = atoi(e);  // 0: no library split
-      if (split && pt > kPartitionTokens) {
-        // the caller's scratch has a partition slot per 512 tokens: coarser partitions use the
-        // first ceil(len / pt) of them
-        p.part_tokens = pt;
-      }
-      if (pt > 0 && (!split || pt < kPartitionTokens)) {
+
+    // ---- split-KV plan.  The kernel cuts the flat list of (head, sequence, cache block)
+    // units into equal ranges by itself, from the real lengths; what the host decides is
+    // where the partials go and how many slots P a (sequence, head) has there, which bounds
+    // how finely the longest sequence can be cut.
+    const int64_t units_hs = int64_t(p.num_seqs) * p.num_kv_heads * p.head_groups;
+    const int64_t pages_max = (int64_t(std::max(a->max_seq_len, 1)) + a->block_size - 1) / a->block_size;
+    const int min_tokens = tune.min_tokens ? tune.min_tokens : 64;
+    const int min_chunk = std::max(2, (min_tokens / a->block_size + 1) & ~1);
+    const int64_t warps_total = int64_t(sm_count()) * warps_for(ring_budget(true));
+    StreamRegion region{};
+    // the unit table lives in shared memory (4 bytes per sequence) and the merge needs one
+    // arrival counter per (sequence, head); batches beyond either have more than enough
+    // sequences to fill the GPU unsplit
+    const bool can_split = table_full <= 48 * 1024 && units_hs <= kArrivePerRegion &&
+                           pages_max > min_chunk && stream_region(s, &region);
+    bool own_ws = false;
+    if (!can_split) {
+      split = false;
+    } else {
+      // slots worth having: the finest cut the kernel would make if the sequences were a
+      // quarter as long as max_seq_len on average (it only knows the bound; skewed batches
+      // have a few long sequences and many short ones)
+      const int64_t c_est = std::max<int64_t>(min_chunk, units_hs * pages_max / 4 / warps_total);
+      const int64_t p_need = std::min<int64_t>(pages_max / c_est + 2, pages_max / min_chunk + 2);
+      const int p_cap = tune.max_parts ? tune.max_parts : 128;
+      // what the stream's region of the library workspace can hold
+      const int64_t per_slot = int64_t(p.num_seqs) * p.num_heads * (8 + int64_t(a->head_size) * 2);
+      int64_t p_ws = (int64_t(region.ws_bytes) - 3 * 256) / std::max<int64_t>(per_slot, 1);
+      p_ws = std::min<int64_t>({p_ws, int64_t(p_cap), pages_max / min_chunk + 2});
+      if (tune.no_split || mode == Scratch::kOwnArray) p_ws = 0;
+      const int64_t p_caller = split ? std::min<int64_t>(a->max_num_partitions, p_cap) : 0;
+      if (p_caller >= 2 && (p_caller >= p_need || p_caller >= p_ws)) {
+        // the layout inside the caller's scratch is the library's business: rows of
+        // p_caller slots (no more than the caller's own row length)
+        p.max_partitions = int(p_caller);
+      } else if (p_ws >= 2) {
+        own_ws = true;
+        split = true;
         auto up = [](int64_t v) { return (v + 255) & ~int64_t(255); };
-        auto need_of = [&](int t) {
-          const int64_t n = int64_t(p.num_seqs) * p.num_heads * parts_of(t);
-          return 2 * up(n * 4) + up(n * a->head_size * 2);
-        };
-        while (pt < kPartitionTokens && need_of(pt) > int64_t(kV1ScratchBytes)) pt *= 2;
-        // fp8 (see above): rather fewer, larger partitions than none at all
-        while (es == 1 && parts_of(pt) > 1 && need_of(pt) > int64_t(kV1ScratchBytes)) pt *= 2;
-        const int64_t parts = parts_of(pt);
-        const int64_t stat = up(int64_t(p.num_seqs) * p.num_heads * parts * 4);
-        unsigned char* ws = ((!split || pt < kPartitionTokens) && parts > 1 &&
-                             need_of(pt) <= int64_t(kV1ScratchBytes) && units <= kArrivePerRegion)
-                                ? v1_scratch_ptr() : nullptr;
-        if (ws != nullptr) {
-          split = true;
-          p.part_tokens = pt;
-          p.max_partitions = int(parts);
-          p.exp_sums = reinterpret_cast<float*>(ws);
-          p.max_logits = reinterpret_cast<float*>(ws + stat);
-          p.tmp_out = ws + 2 * stat;
-        }
+        const int64_t stat = up(int64_t(p.num_seqs) * p.num_heads * p_ws * 4);
+        p.max_partitions = int(p_ws);
+        p.exp_sums = reinterpret_cast<float*>(region.ws);
+        p.max_logits = reinterpret_cast<float*>(region.ws + stat);
+        p.tmp_out = region.ws + 2 * stat;
+      } else {
+        split = false;
       }
     }
-    // The partition table of a split launch lives in shared memory (4 bytes per sequence).
-    // Batches it cannot hold have more than enough sequences to fill the GPU unsplit.
-    if (split && size_t((p.num_seqs + 1 + 3) & ~3) * 4 > 48 * 1024) {
-      split = false;
+    if (split) {
+      // lengths beyond what the caller's scratch was sized for are ignored, like the
+      // reference's v2 grid ignores partitions beyond max_num_partitions
+      if (!own_ws && mode == Scratch::kCaller)
+        p.len_cap = int(std::min<int64_t>(int64_t(a->max_num_partitions) * kPartitionTokens, INT32_MAX));
+    } else {
       p.max_partitions = 0;
     }
-    // lengths beyond what the scratch has partitions for are ignored, like the reference's v2
-    // grid ignores partitions beyond max_num_partitions
-    // (the caller's scratch covers max_partitions * 512 tokens whatever the partition size)
-    const int slot_tokens = p.exp_sums == a->exp_sums ? std::min(p.part_tokens, kPartitionTokens)
-                                                      : p.part_tokens;
-    p.len_cap = split ? int(std::min<int64_t>(int64_t(p.max_partitions) * slot_tokens, INT32_MAX))
-                      : INT32_MAX;
     p.use_table = split ? 1 : 0;
-    const size_t table_bytes = p.use_table ? size_t((p.num_seqs + 1 + 3) & ~3) * 4 : 0;
-    if (table_bytes > 48 * 1024) {
-      set_error("num_seqs=%d is too large for the split-KV partition table", a->num_seqs);
-      return B200PA_EUNSUPPORTED;
-    }
-    const size_t budget = ring_budget(p.use_table != 0);
-    // B200PA_TUNE_WARPS / B200PA_TUNE_STAGES override (STAGES = slots per warp).
+    p.min_chunk = min_chunk;
+    const size_t table_bytes = split ? table_full : 0;
+    const size_t budget = ring_budget(split);
     int nwarps = warps_for(budget);
-    if (const char* e = getenv("B200PA_TUNE_WARPS"))
-      nwarps = std::max(1, std::min(ki.max_warps, atoi(e)));
-    // Launches with fewer work items than warps are bound by the latency of one item, not by
-    // bandwidth: run just enough warps to give every item its own (a multiple of 4, at least
-    // 4) and spend the shared memory on a deeper ring (<= 8 slots) so that one warp keeps
-    // many pages in flight.
+    if (tune.warps) nwarps = std::max(1, std::min(ki.max_warps, tune.warps));
+    // Ring slots per warp: two.  Measured on B200, a launch with work for every warp is 3-5 %
+    // slower when the CTA is given shared memory for four slots per warp, even if only two of
+    // them are kept in flight; a split launch whose batch turns out to have fewer ranges than
+    // the grid has warps deepens the rings of its busy warps by itself with the slots of the
+    // idle ones.  Unsplit launches with fewer work items than warps are bound by the latency of
+    // one item: just enough warps to give every item its own (a multiple of 4, at least 4) and
+    // the shared memory spent on a deeper ring (<= 8 slots).
     int ns = 2;
-    {
-      const int64_t parts_ub =
-          split ? std::max<int64_t>(1, (int64_t(a->max_seq_len) + p.part_tokens - 1) / p.part_tokens) : 1;
-      const int64_t items_ub = int64_t(p.num_seqs) * p.num_kv_heads * p.head_groups * parts_ub;
-      if (items_ub <= int64_t(sm_count()) * nwarps && !getenv("B200PA_TUNE_WARPS")) {
-        const int need = int((items_ub + sm_count() - 1) / sm_count());
+    if (!split) {
+      const int64_t items = units_hs;
+      if (items <= int64_t(sm_count()) * nwarps && !tune.warps) {
+        const int need = int((items + sm_count() - 1) / sm_count());
         nwarps = std::min(nwarps, std::max(4, (need + 3) & ~3));
         ns = 8;
       }
     }
     ns = int(std::min<size_t>(size_t(ns), budget / (size_t(nwarps) * slot_bytes)));
-    if (const char* e = getenv("B200PA_TUNE_STAGES"))
-      ns = std::max(int(min_slots), std::min(int(budget / (size_t(nwarps) * slot_bytes)), atoi(e)));
+    if (tune.stages)
+      ns = std::max(int(min_slots), std::min(int(budget / (size_t(nwarps) * slot_bytes)), tune.stages));
     if (ns < int(min_slots)) {
       set_error("head_size=%d block_size=%d does not fit the shared-memory pipeline", a->head_size,
                 a->block_size);
       return B200PA_EUNSUPPORTED;
     }
     p.nstages = ns;
-    unsigned* arrive = nullptr;
     p.status = device_status_ptr();
-    if (!launch_slots(&p.sched, &arrive) || p.status == nullptr) {
+    p.sched = sched_words();
+    if (p.sched == nullptr || p.status == nullptr) {
       set_error("could not resolve device-side scheduler/status words");
       return B200PA_ECUDA;
     }
-    // merge the partials inside the decode kernel when the counters cover the batch
-    fused = split && int64_t(p.num_seqs) * p.num_kv_heads * p.head_groups <= kArrivePerRegion;
-    p.arrive = fused ? arrive : nullptr;
+    // the partials are merged inside the decode kernel
+    fused = split;
+    p.arrive = fused ? region.arrive : nullptr;
+    // sequences cut into many pieces are merged in two levels when there are counters for the
+    // groups of every (sequence, head)
+    p.groups_max = (p.max_partitions + kMergeFan - 1) / kMergeFan;
+    p.arrive2 = (fused && p.max_partitions > kMergeDirectMax &&
+                 units_hs * p.groups_max <= kArrive2PerRegion) ? region.arrive2 : nullptr;
     const size_t bars_bytes = (size_t(nwarps) * ns * 8 + 127) & ~size_t(127);
     const size_t smem = table_bytes + bars_bytes + size_t(nwarps) * ns * slot_bytes;
     const int grid = sm_count();
@@ -631,11 +718,11 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, bool v2) {
 }  // namespace b200pa
 
 extern "C" int b200pa_paged_attention_v1(const b200pa_attn_args* args, void* stream) {
-  return b200pa::attention_entry(args, stream, false);
+  return b200pa::attention_entry(args, stream, b200pa::Scratch::kNone);
 }
 
 extern "C" int b200pa_paged_attention_v2(const b200pa_attn_args* args, void* stream) {
-  return b200pa::attention_entry(args, stream, true);
+  return b200pa::attention_entry(args, stream, b200pa::Scratch::kCaller);
 }
 
 // ------------------------------------------------------------------ v2 without caller scratch
@@ -646,7 +733,7 @@ extern "C" int b200pa_paged_attention_v2(const b200pa_attn_args* args, void* str
 // file-scope device array: every GPU that loads the library holds these 32 MiB
 // until the process exits.  All calls on a device share it and it keeps the
 // previous call's contents; nothing in it has to start at zero, because the
-// decode kernel writes every partial (m, l, O) that the reduce kernel reads.
+// decode kernel writes every partial (m, l, O) that the merge reads.
 namespace b200pa {
 
 constexpr size_t kBuiltinScratchBytes = size_t(32) << 20;
@@ -685,47 +772,55 @@ extern "C" int b200pa_paged_attention_v2_noalloc(const b200pa_attn_args* args, v
                        args->max_seq_len >= 0,
                    "bad sizes: num_seqs=%d num_heads=%d head_size=%d max_seq_len=%d", args->num_seqs,
                    args->num_heads, args->head_size, args->max_seq_len);
+  // the documented limit: one partial slot per 512 tokens of max_seq_len has to fit
   const int64_t parts = std::max<int64_t>(
       1, (int64_t(args->max_seq_len) + kPartitionTokens - 1) / kPartitionTokens);
-  const int64_t n = int64_t(args->num_seqs) * args->num_heads * parts;
+  const int64_t rows = int64_t(args->num_seqs) * args->num_heads;
   const int64_t esize = args->q_dtype == B200PA_F32 ? 4 : 2;
   auto up = [](int64_t v) { return (v + 255) & ~int64_t(255); };
-  const int64_t stat_bytes = up(n * 4);
-  const int64_t need = 2 * stat_bytes + up(n * args->head_size * esize);
-  if (need > int64_t(kBuiltinScratchBytes)) {
+  auto need_of = [&](int64_t slots) {
+    return 2 * up(rows * slots * 4) + up(rows * slots * args->head_size * esize);
+  };
+  if (need_of(parts) > int64_t(kBuiltinScratchBytes)) {
     set_error("paged_attention_v2_noalloc: num_seqs=%d x num_heads=%d x %lld partitions needs %lld "
               "bytes of split-KV scratch, the built-in buffer holds %lld; use "
               "b200pa_paged_attention_v2 with caller scratch",
-              args->num_seqs, args->num_heads, (long long)parts, (long long)need,
+              args->num_seqs, args->num_heads, (long long)parts, (long long)need_of(parts),
               (long long)kBuiltinScratchBytes);
     return B200PA_EINVAL;
   }
   unsigned char* base = builtin_scratch_ptr();
   if (base == nullptr) return B200PA_ECUDA;
+  // Room left in the array becomes more slots per (sequence, head): a small batch of long
+  // sequences can then be cut finer than one piece per 512 tokens.
+  int64_t slots = parts;
+  while (slots < 128 && need_of(slots * 2) <= int64_t(kBuiltinScratchBytes)) slots *= 2;
+  const int64_t stat_bytes = up(rows * slots * 4);
   b200pa_attn_args a = *args;
   a.exp_sums = reinterpret_cast<float*>(base);
   a.max_logits = reinterpret_cast<float*>(base + stat_bytes);
   a.tmp_out = base + 2 * stat_bytes;
-  a.max_num_partitions = static_cast<int32_t>(parts);
-  return attention_entry(&a, stream, true);
+  a.max_num_partitions = static_cast<int32_t>(slots);
+  return attention_entry(&a, stream, Scratch::kOwnArray);
 }
 
 extern "C" int b200pa_reset_device_state(void* stream) {
   using namespace b200pa;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  unsigned* sched = nullptr;
-  unsigned* arrive = nullptr;
   int* status = device_status_ptr();
-  if (!launch_slots(&sched, &arrive) || status == nullptr) {
-    set_error("could not resolve device-side scheduler/status words");
+  if (status == nullptr) {
+    set_error("could not resolve the device-side status word");
     return B200PA_ECUDA;
   }
   void* sbase = nullptr;
   void* abase = nullptr;
   B200PA_CHECK_CUDA(cudaGetSymbolAddress(&sbase, g_sched_words));
+  void* a2base = nullptr;
   B200PA_CHECK_CUDA(cudaGetSymbolAddress(&abase, g_arrive));
+  B200PA_CHECK_CUDA(cudaGetSymbolAddress(&a2base, g_arrive2));
   B200PA_CHECK_CUDA(cudaMemsetAsync(sbase, 0, sizeof(g_sched_words), s));
   B200PA_CHECK_CUDA(cudaMemsetAsync(abase, 0, sizeof(g_arrive), s));
+  B200PA_CHECK_CUDA(cudaMemsetAsync(a2base, 0, sizeof(g_arrive2), s));
   B200PA_CHECK_CUDA(cudaMemsetAsync(status, 0, sizeof(int), s));
   return B200PA_OK;
 }

@@ -6,16 +6,17 @@
 //
 // Operator schemas are byte-for-byte those of the reference
 // (csrc/torch_bindings.cpp:52-76, :687-704, :716-719).  The ops are always
-// registered as torch.ops._C_b200.* / torch.ops._C_b200_cache_ops.*; when no
-// other library has defined torch.ops._C.paged_attention_v1 etc. they are also
-// registered under the reference's own names (_C / _C_cache_ops), so code
-// written against vllm._custom_ops runs unchanged.
+// registered as torch.ops._C_b200.* / torch.ops._C_b200_cache_ops.*; on request
+// (b200_claim_reference_names) also under the reference's own names
+// (_C / _C_cache_ops), so code written against vllm._custom_ops runs unchanged.
 #include <ATen/core/dispatch/Dispatcher.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 #include <torch/all.h>
 #include <torch/library.h>
 
+#include <cstdio>
+#include <memory>
 #include <optional>
 #include <string>
 #include <vector>
@@ -471,41 +472,65 @@ TORCH_LIBRARY(_C_b200_cache_ops, cache_ops) {
   cache_ops.impl("convert_fp8", torch::kCUDA, &convert_fp8);
 }
 
-// The reference's own operator names, claimed only when nobody defined them yet.
-TORCH_LIBRARY_FRAGMENT(_C, ops) {
-  if (!op_exists("_C::paged_attention_v1")) {
-    ops.def(kV1Schema);
-    ops.impl("paged_attention_v1", torch::kCUDA, &paged_attention_v1);
-  }
-  if (!op_exists("_C::paged_attention_v2")) {
-    ops.def(kV2Schema);
-    ops.impl("paged_attention_v2", torch::kCUDA, &paged_attention_v2);
-  }
-  if (!op_exists("_C::merge_attn_states")) {
-    ops.def(kMergeSchema);
-    ops.impl("merge_attn_states", torch::kCUDA, &merge_attn_states);
-  }
-}
-
-TORCH_LIBRARY_FRAGMENT(_C_cache_ops, cache_ops) {
-  if (!op_exists("_C_cache_ops::reshape_and_cache")) {
-    cache_ops.def(kReshapeSchema);
-    cache_ops.impl("reshape_and_cache", torch::kCUDA, &reshape_and_cache);
-  }
-  if (!op_exists("_C_cache_ops::reshape_and_cache_flash")) {
-    cache_ops.def(kReshapeFlashSchema);
-    cache_ops.impl("reshape_and_cache_flash", torch::kCUDA, &reshape_and_cache_flash);
-  }
-  if (!op_exists("_C_cache_ops::swap_blocks")) {
-    cache_ops.def(kSwapSchema);
-    cache_ops.impl("swap_blocks", torch::kCUDA, &swap_blocks);
-  }
-  if (!op_exists("_C_cache_ops::copy_blocks")) {
-    cache_ops.def(kCopySchema);
-    cache_ops.impl("copy_blocks", torch::kCUDA, &copy_blocks);
-  }
-  if (!op_exists("_C_cache_ops::convert_fp8")) {
-    cache_ops.def(kConvertSchema);
-    cache_ops.impl("convert_fp8", torch::kCUDA, &convert_fp8);
+// The reference's own operator names (_C / _C_cache_ops) are claimed on request only, never
+// while this library loads: if they were defined here first, a vLLM `_C` extension imported
+// afterwards would fail on the duplicate definitions.  A stand-alone user (the reference's
+// own tests and benchmarks run without vLLM's extension) asks for them once with
+// vllm_b200.claim_reference_names(); names that somebody has defined already are left alone.
+// Returns how many names were claimed by this call, or -1 with `err` filled in.
+extern "C" int b200_claim_reference_names(char* err, int err_len) {
+  static std::vector<std::unique_ptr<torch::Library>> keep;  // registrations live as long as these
+  try {
+    int n = 0;
+    auto ops = std::make_unique<torch::Library>(torch::Library::FRAGMENT, "_C", std::nullopt,
+                                                __FILE__, __LINE__);
+    auto cache_ops = std::make_unique<torch::Library>(torch::Library::FRAGMENT, "_C_cache_ops",
+                                                      std::nullopt, __FILE__, __LINE__);
+    if (!op_exists("_C::paged_attention_v1")) {
+      ops->def(kV1Schema);
+      ops->impl("paged_attention_v1", torch::kCUDA, &paged_attention_v1);
+      ++n;
+    }
+    if (!op_exists("_C::paged_attention_v2")) {
+      ops->def(kV2Schema);
+      ops->impl("paged_attention_v2", torch::kCUDA, &paged_attention_v2);
+      ++n;
+    }
+    if (!op_exists("_C::merge_attn_states")) {
+      ops->def(kMergeSchema);
+      ops->impl("merge_attn_states", torch::kCUDA, &merge_attn_states);
+      ++n;
+    }
+    if (!op_exists("_C_cache_ops::reshape_and_cache")) {
+      cache_ops->def(kReshapeSchema);
+      cache_ops->impl("reshape_and_cache", torch::kCUDA, &reshape_and_cache);
+      ++n;
+    }
+    if (!op_exists("_C_cache_ops::reshape_and_cache_flash")) {
+      cache_ops->def(kReshapeFlashSchema);
+      cache_ops->impl("reshape_and_cache_flash", torch::kCUDA, &reshape_and_cache_flash);
+      ++n;
+    }
+    if (!op_exists("_C_cache_ops::swap_blocks")) {
+      cache_ops->def(kSwapSchema);
+      cache_ops->impl("swap_blocks", torch::kCUDA, &swap_blocks);
+      ++n;
+    }
+    if (!op_exists("_C_cache_ops::copy_blocks")) {
+      cache_ops->def(kCopySchema);
+      cache_ops->impl("copy_blocks", torch::kCUDA, &copy_blocks);
+      ++n;
+    }
+    if (!op_exists("_C_cache_ops::convert_fp8")) {
+      cache_ops->def(kConvertSchema);
+      cache_ops->impl("convert_fp8", torch::kCUDA, &convert_fp8);
+      ++n;
+    }
+    keep.push_back(std::move(ops));
+    keep.push_back(std::move(cache_ops));
+    return n;
+  } catch (const std::exception& e) {
+    if (err != nullptr && err_len > 0) snprintf(err, size_t(err_len), "%s", e.what());
+    return -1;
   }
 }
