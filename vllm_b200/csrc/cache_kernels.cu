@@ -7,14 +7,18 @@
 //   * x-layout K: one 16-byte store per (token, head, d/x) chunk.
 //   * x-layout V is a transpose ([token][d] -> [d][token-in-block]).  A CTA owns
 //     a tile of 16 consecutive tokens.  When the tile fills 16 consecutive slots
-//     of one block (prefill, chunked writes) a thread reads 16 bytes of 8 d per
-//     token and writes 8 rows of 16 tokens with 16-byte stores; otherwise each
-//     thread owns one (head, d) row and writes every run of tokens that landed
-//     in consecutive slots with the widest aligned store, instead of one
-//     1-2 byte store per element.
+//     of one block (prefill, chunked writes) a thread reads 8 bytes of 4 d per
+//     token and writes 4 rows of 16 tokens with 16-byte stores; otherwise each
+//     thread owns one (head, d) row, reads its element of all 16 tokens at once
+//     and writes four bytes at a time wherever tokens landed in consecutive,
+//     aligned slots, instead of one 1-2 byte store per element.
 //   * flash layout: 16-byte vector row copies, NHD or HND by strides.
 // Quantisation is cvt.rn.satfinite of the correctly rounded fp32 quotient x / scale,
 // bit-identical to the reference's scaled_convert (quant_utils.cuh:469-502).
+#include <algorithm>
+#include <cstdlib>
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace b200pa {
@@ -26,41 +30,41 @@ enum : int { kKvAuto = 0, kKvE4M3 = 1, kKvE5M2 = 2 };
 // XU-bound; here the reciprocal is taken once and each quotient is the product x * r followed
 // by two residual corrections q += fma(-q, s, x) * r.  The first leaves q within one ulp, the
 // second then yields the correctly rounded quotient (Markstein's theorem; r is the correctly
-// rounded reciprocal).  Only used while nothing can overflow or lose residual bits to
-// underflow: scales within 2^+-60 and 2^-20 <= |q| < 2^17.  Outside that window the plain
-// product x * r is returned: larger quotients saturate in both fp8 formats and smaller ones
-// round to zero whatever their last bits are (the product also keeps the sign of a zero and
-// passes inf / NaN through, which the corrections would not).  Other scales use the division.
+// rounded reciprocal).  Used for positive scales within 2^+-60: there a residual can only
+// lose bits to underflow for |x / s| < 2^-42, which is zero in both fp8 formats whatever its
+// last bits are.  Other scales use the division.
 struct ScaledDiv {
   float s, r;
   bool fast;
+  uint64_t s2, nr2;  // {s, s} and {-r, -r} for the packed fp32 pipe
   __device__ __forceinline__ explicit ScaledDiv(float scale) : s(scale) {
     r = __fdiv_rn(1.f, scale);
-    const float a = fabsf(scale);
-    fast = a >= 0x1p-60f && a <= 0x1p60f;
+    fast = scale >= 0x1p-60f && scale <= 0x1p60f;
+    const float nr = -r;
+    asm("mov.b64 %0, {%1, %1};" : "=l"(s2) : "f"(s));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(nr2) : "f"(nr));
   }
-  // Two quotients at once on the packed fp32 pipe (fma.rn.f32x2, sm_100).
+  // MINUS the two quotients, on the packed fp32 pipe (fma.rn.f32x2, sm_100).  The sequence
+  // runs on the negated quotient q' = -x/s because that keeps the sign of a zero:
+  //   q' = x * (-r);  e = fma(q', s, x) = x - q*s;  q' = fma(e, -r, q')
+  // gives q' = -0 for x = +0 and +0 for x = -0, where the same steps on q itself turn -0
+  // into +0.  The caller flips the sign bit of the fp8 codes instead (one XOR per four
+  // codes).  An infinite or overflowing quotient comes out as NaN (inf - inf); the caller
+  // sees its NaN code and redoes those elements with the division.
   // Callers check `fast` once per kernel, not per pair.
-  __device__ __forceinline__ void pair(float x0, float x1, float& o0, float& o1) const {
-    float p0, p1, c0, c1;
+  __device__ __forceinline__ void neg_pair(float x0, float x1, float& o0, float& o1) const {
     asm("{\n"
-        " .reg .b64 x, r, ns, q, e;\n"
-        " mov.b64 x, {%4, %5};\n"
-        " mov.b64 r, {%6, %6};\n"
-        " mov.b64 ns, {%7, %7};\n"
-        " mul.rn.f32x2 q, x, r;\n"
+        " .reg .b64 x, q, e;\n"
+        " mov.b64 x, {%2, %3};\n"
+        " mul.rn.f32x2 q, x, %4;\n"
+        " fma.rn.f32x2 e, q, %5, x;\n"
+        " fma.rn.f32x2 q, e, %4, q;\n"
+        " fma.rn.f32x2 e, q, %5, x;\n"
+        " fma.rn.f32x2 q, e, %4, q;\n"
         " mov.b64 {%0, %1}, q;\n"
-        " fma.rn.f32x2 e, q, ns, x;\n"
-        " fma.rn.f32x2 q, e, r, q;\n"
-        " fma.rn.f32x2 e, q, ns, x;\n"
-        " fma.rn.f32x2 q, e, r, q;\n"
-        " mov.b64 {%2, %3}, q;\n"
         "}"
-        : "=f"(p0), "=f"(p1), "=f"(c0), "=f"(c1)
-        : "f"(x0), "f"(x1), "f"(r), "f"(-s));
-    const float a0 = fabsf(p0), a1 = fabsf(p1);
-    o0 = (a0 >= 0x1p-20f && a0 < 0x1p17f) ? c0 : p0;
-    o1 = (a1 >= 0x1p-20f && a1 < 0x1p17f) ? c1 : p1;
+        : "=f"(o0), "=f"(o1)
+        : "f"(x0), "f"(x1), "l"(nr2), "l"(s2));
   }
   __device__ __forceinline__ float operator()(float x) const {
     if (!fast) return __fdiv_rn(x, s);
@@ -72,62 +76,131 @@ struct ScaledDiv {
   }
 };
 
-template <typename in_t, typename cache_t, int KV>
-__device__ __forceinline__ cache_t store_convert(in_t v, const ScaledDiv& div) {
-  if constexpr (KV == kKvAuto) {
-    return v;
+// Four 16-bit inputs (two 32-bit words of two elements each) -> four fp8 codes of MINUS the
+// quotients x / s (ScaledDiv::neg_pair explains the sign), in one asm block so that the
+// packed-fp32 register pairs are formed where the values are produced and no moves are
+// needed around the packed instructions.
+template <typename in_t, bool kE5M2>
+__device__ __forceinline__ uint32_t neg_quant4(uint32_t w0, uint32_t w1, const ScaledDiv& div) {
+  uint32_t out;
+  if constexpr (std::is_same_v<in_t, __nv_bfloat16>) {
+    if constexpr (kE5M2) {
+      asm("{\n"
+          " .reg .b32 a0, a1, b0, b1;\n"
+          " .reg .b64 x, y, q, r, e;\n"
+          " .reg .b16 lo, hi;\n"
+          " shl.b32 a0, %1, 16;\n and.b32 a1, %1, 0xffff0000;\n"
+          " shl.b32 b0, %2, 16;\n and.b32 b1, %2, 0xffff0000;\n"
+          " mov.b64 x, {a0, a1};\n mov.b64 y, {b0, b1};\n"
+          " mul.rn.f32x2 q, x, %3;\n mul.rn.f32x2 r, y, %3;\n"
+          " fma.rn.f32x2 e, q, %4, x;\n fma.rn.f32x2 q, e, %3, q;\n"
+          " fma.rn.f32x2 e, r, %4, y;\n fma.rn.f32x2 r, e, %3, r;\n"
+          " fma.rn.f32x2 e, q, %4, x;\n fma.rn.f32x2 q, e, %3, q;\n"
+          " fma.rn.f32x2 e, r, %4, y;\n fma.rn.f32x2 r, e, %3, r;\n"
+          " mov.b64 {a0, a1}, q;\n mov.b64 {b0, b1}, r;\n"
+          " cvt.rn.satfinite.e5m2x2.f32 lo, a1, a0;\n"
+          " cvt.rn.satfinite.e5m2x2.f32 hi, b1, b0;\n"
+          " mov.b32 %0, {lo, hi};\n"
+          "}"
+          : "=r"(out)
+          : "r"(w0), "r"(w1), "l"(div.nr2), "l"(div.s2));
+    } else {
+      asm("{\n"
+          " .reg .b32 a0, a1, b0, b1;\n"
+          " .reg .b64 x, y, q, r, e;\n"
+          " .reg .b16 lo, hi;\n"
+          " shl.b32 a0, %1, 16;\n and.b32 a1, %1, 0xffff0000;\n"
+          " shl.b32 b0, %2, 16;\n and.b32 b1, %2, 0xffff0000;\n"
+          " mov.b64 x, {a0, a1};\n mov.b64 y, {b0, b1};\n"
+          " mul.rn.f32x2 q, x, %3;\n mul.rn.f32x2 r, y, %3;\n"
+          " fma.rn.f32x2 e, q, %4, x;\n fma.rn.f32x2 q, e, %3, q;\n"
+          " fma.rn.f32x2 e, r, %4, y;\n fma.rn.f32x2 r, e, %3, r;\n"
+          " fma.rn.f32x2 e, q, %4, x;\n fma.rn.f32x2 q, e, %3, q;\n"
+          " fma.rn.f32x2 e, r, %4, y;\n fma.rn.f32x2 r, e, %3, r;\n"
+          " mov.b64 {a0, a1}, q;\n mov.b64 {b0, b1}, r;\n"
+          " cvt.rn.satfinite.e4m3x2.f32 lo, a1, a0;\n"
+          " cvt.rn.satfinite.e4m3x2.f32 hi, b1, b0;\n"
+          " mov.b32 %0, {lo, hi};\n"
+          "}"
+          : "=r"(out)
+          : "r"(w0), "r"(w1), "l"(div.nr2), "l"(div.s2));
+    }
   } else {
-    return f32_to_fp8<KV == kKvE5M2>(div(to_f32(v)));
+    const __half2 h0 = *reinterpret_cast<const __half2*>(&w0);
+    const __half2 h1 = *reinterpret_cast<const __half2*>(&w1);
+    float q0, q1, q2, q3;
+    div.neg_pair(__low2float(h0), __high2float(h0), q0, q1);
+    div.neg_pair(__low2float(h1), __high2float(h1), q2, q3);
+    out = uint32_t(f32x2_to_fp8x2<kE5M2>(q0, q1)) | (uint32_t(f32x2_to_fp8x2<kE5M2>(q2, q3)) << 16);
   }
+  return out;
 }
 
-// N consecutive elements; fp8 conversions go two at a time (one cvt for a byte pair).
+// N consecutive elements.  fp8: four at a time - two pair conversions of the negated
+// quotients, sign bits flipped back in the assembled word; a group of up to 16 codes that holds
+// a NaN code (a NaN, or a quotient that overflowed inside neg_pair) is redone with the division,
+// which is rare.
 template <typename in_t, typename cache_t, int KV, int N>
 __device__ __forceinline__ void convert_n(const in_t (&in)[N], cache_t* out, const ScaledDiv& div) {
   if constexpr (KV == kKvAuto) {
 #pragma unroll
     for (int i = 0; i < N; ++i) out[i] = in[i];
-  } else {
-    static_assert(N % 2 == 0, "pairs");
+  } else if constexpr (N % 4 == 0) {
+    constexpr bool kE5 = KV == kKvE5M2;
+    if (!div.fast) {  // the same for every thread of the launch
 #pragma unroll
-    for (int i = 0; i < N; i += 2) {
-      float q0, q1;
-      div.pair(to_f32(in[i]), to_f32(in[i + 1]), q0, q1);
-      const uint16_t two = f32x2_to_fp8x2<KV == kKvE5M2>(q0, q1);
-      out[i] = static_cast<cache_t>(two & 0xFF);
-      out[i + 1] = static_cast<cache_t>(two >> 8);
+      for (int i = 0; i < N; ++i) out[i] = f32_to_fp8<kE5>(__fdiv_rn(to_f32(in[i]), div.s));
+      return;
     }
+    uint32_t w[N / 4];
+    uint32_t nan_bits = 0;
+#pragma unroll
+    for (int i = 0; i < N; i += 4) {
+      uint32_t v;
+      if constexpr (sizeof(in_t) == 2) {
+        uint32_t w0, w1;
+        const uint16_t b0 = *reinterpret_cast<const uint16_t*>(&in[i]);
+        const uint16_t b1 = *reinterpret_cast<const uint16_t*>(&in[i + 1]);
+        const uint16_t b2 = *reinterpret_cast<const uint16_t*>(&in[i + 2]);
+        const uint16_t b3 = *reinterpret_cast<const uint16_t*>(&in[i + 3]);
+        w0 = uint32_t(b0) | (uint32_t(b1) << 16);
+        w1 = uint32_t(b2) | (uint32_t(b3) << 16);
+        v = neg_quant4<in_t, kE5>(w0, w1, div);
+      } else {
+        float q0, q1, q2, q3;
+        div.neg_pair(to_f32(in[i]), to_f32(in[i + 1]), q0, q1);
+        div.neg_pair(to_f32(in[i + 2]), to_f32(in[i + 3]), q2, q3);
+        v = uint32_t(f32x2_to_fp8x2<kE5>(q0, q1)) | (uint32_t(f32x2_to_fp8x2<kE5>(q2, q3)) << 16);
+      }
+      // a byte whose low seven bits are all ones is a NaN code in both formats
+      nan_bits |= ((v & 0x7F7F7F7Fu) + 0x01010101u) & 0x80808080u;
+      w[i / 4] = v ^ 0x80808080u;
+    }
+    if (nan_bits != 0) {
+#pragma unroll
+      for (int i = 0; i < N; i += 4) {
+        uint32_t v = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          v |= uint32_t(f32_to_fp8<kE5>(__fdiv_rn(to_f32(in[i + k]), div.s))) << (8 * k);
+        w[i / 4] = v;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < N / 4; ++i) reinterpret_cast<uint32_t*>(out)[i] = w[i];
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) out[i] = f32_to_fp8<KV == kKvE5M2>(div(to_f32(in[i])));
   }
 }
+
+}  // namespace b200pa
+
+#include "kv_write_staged.cuh"
+
+namespace b200pa {
 
 constexpr int kTokTile = 16;
-
-// Widest store that the address and byte count allow.
-template <typename cache_t, int N>
-__device__ __forceinline__ void store_run(cache_t* dst, const cache_t (&vals)[N], int len) {
-  const uintptr_t a = reinterpret_cast<uintptr_t>(dst);
-  const int bytes = len * int(sizeof(cache_t));
-  if (((a | bytes) & 15) == 0) {
-    const uint4* src = reinterpret_cast<const uint4*>(vals);
-#pragma unroll
-    for (int i = 0; i < int(N * sizeof(cache_t) / 16); ++i)
-      if (i * 16 < bytes) reinterpret_cast<uint4*>(dst)[i] = src[i];
-  } else if (((a | bytes) & 7) == 0) {
-    const uint2* src = reinterpret_cast<const uint2*>(vals);
-#pragma unroll
-    for (int i = 0; i < int(N * sizeof(cache_t) / 8); ++i)
-      if (i * 8 < bytes) reinterpret_cast<uint2*>(dst)[i] = src[i];
-  } else if (((a | bytes) & 3) == 0) {
-    const uint32_t* src = reinterpret_cast<const uint32_t*>(vals);
-#pragma unroll
-    for (int i = 0; i < int(N * sizeof(cache_t) / 4); ++i)
-      if (i * 4 < bytes) reinterpret_cast<uint32_t*>(dst)[i] = src[i];
-  } else {
-#pragma unroll
-    for (int i = 0; i < N; ++i)
-      if (i < len) dst[i] = vals[i];
-  }
-}
 
 // n / d for small operands (n * d < 2^32) by one multiply-high with a precomputed factor:
 // the index arithmetic below would otherwise spend more instructions on runtime divisions
@@ -143,16 +216,21 @@ struct SmallDiv {
 };
 
 // Per-tile set-up shared by both layouts: cache block and offset of each of the tile's
-// tokens (block -1 = padding token, skipped), and whether the tile fills 16 consecutive
-// slots that start at a multiple of 16 (true for prefill and chunked writes).
+// tokens (block -1 = padding token, skipped), whether the tile fills 16 consecutive slots
+// that start at a multiple of 16 (true for prefill and chunked writes whose sequences start
+// on a tile boundary), and for every other tile how its tokens go into a V row of the
+// x-layout: `cnt[t]` = 0 when token t is written together with an earlier one, else the
+// number of tokens from t on that sit in consecutive slots at a 4-byte aligned address and
+// fill one 4-byte store (4 / element size), else 1.
 struct TileSlots {
   int64_t blk[kTokTile];
   int off[kTokTile];
+  int cnt[kTokTile];
   int full_run;
 };
 
 __device__ __forceinline__ void load_tile_slots(TileSlots& ts, const int64_t* __restrict__ slot_mapping,
-                                                int tok0, int ntok, int block_size) {
+                                                int tok0, int ntok, int block_size, int elem_size) {
   if (threadIdx.x < 32) {
     const int t = threadIdx.x;
     const int64_t slot = t < ntok ? slot_mapping[tok0 + t] : int64_t(-1);
@@ -167,6 +245,28 @@ __device__ __forceinline__ void load_tile_slots(TileSlots& ts, const int64_t* __
     if (t == 0)
       ts.full_run = all && ntok == kTokTile && s0 >= 0 && s0 % kTokTile == 0 &&
                     block_size % kTokTile == 0;
+    // 4-byte groups: token t can start one when its slot is 4-byte aligned inside a block whose
+    // rows are (block_size * elem_size is a multiple of 4 for every supported block size) and
+    // the next w - 1 tokens follow in the same block
+    const int w = elem_size >= 4 ? 1 : 4 / elem_size;
+    bool start = false;
+    if (w > 1) {
+      const int64_t b = slot >= 0 ? slot / block_size : int64_t(-1);
+      const int off = slot >= 0 ? int(slot - b * block_size) : 0;
+      bool follows = true;  // tokens t+1 .. t+w-1 continue t's run inside its block
+      for (int k = 1; k < w; ++k) {
+        const int64_t sk = __shfl_down_sync(0xffffffffu, slot, k);
+        follows &= (t + k < kTokTile) && sk == slot + k;
+      }
+      start = slot >= 0 && follows && (off * elem_size) % 4 == 0 && off + w <= block_size &&
+              (block_size * elem_size) % 4 == 0;
+    }
+    // groups cannot overlap (two starts inside one run are at least w tokens apart, because
+    // both are aligned): a token is covered when one of the w - 1 tokens before it starts one
+    const unsigned starts = __ballot_sync(0xffffffffu, start);
+    unsigned covered = 0;
+    for (int k = 1; k < w; ++k) covered |= starts << k;
+    if (t < kTokTile) ts.cnt[t] = ((starts >> t) & 1u) ? w : (((covered >> t) & 1u) ? 0 : 1);
   }
   __syncthreads();
 }
@@ -200,9 +300,48 @@ __device__ __noinline__ void reshape_tile_generic(const TileSlots& ts, const in_
   }
 }
 
-// grid.x = ceil(num_tokens / kTokTile); block = 256 threads.
+// V of every tile that is not 16 aligned consecutive slots (decode steps: each token in a
+// block of its own; prefill whose sequences do not start on a tile boundary: runs of
+// consecutive slots).  A thread owns one (head, d) row: it reads the row's element of every
+// token of the tile (independent loads, adjacent threads adjacent addresses), converts them,
+// and stores them as the tile's plan says - four bytes at a time where consecutive tokens
+// allow it, else one element.  Out of line: it must not cost the common path registers.
 template <typename in_t, typename cache_t, int KV>
-__global__ void __launch_bounds__(256)
+__device__ __noinline__ void reshape_tile_v_general(const TileSlots& ts, const in_t* __restrict__ value,
+                                                    cache_t* __restrict__ value_cache,
+                                                    int64_t value_stride, int tok0, int ntok, int h0,
+                                                    int nh, int head_size, int hd, int block_size,
+                                                    const ScaledDiv& v_scale) {
+  constexpr int W4 = sizeof(cache_t) >= 4 ? 1 : 4 / int(sizeof(cache_t));  // tokens per 4-byte store
+  for (int row = h0 * head_size + threadIdx.x; row < (h0 + nh) * head_size; row += blockDim.x) {
+    const in_t* src = value + int64_t(tok0) * value_stride + row;
+    in_t raw[kTokTile];
+#pragma unroll
+    for (int t = 0; t < kTokTile; ++t)
+      raw[t] = (t < ntok && ts.blk[t] >= 0) ? src[int64_t(t) * value_stride] : in_t(0.f);
+    __align__(16) cache_t conv[kTokTile];
+    convert_n<in_t, cache_t, KV, kTokTile>(raw, conv, v_scale);
+#pragma unroll
+    for (int t = 0; t < kTokTile; ++t) {
+      const int n = ts.cnt[t];  // the same for every thread of the CTA
+      if (n == 0 || t >= ntok || ts.blk[t] < 0) continue;
+      cache_t* dst = value_cache + (ts.blk[t] * hd + row) * int64_t(block_size) + ts.off[t];
+      if (W4 > 1 && n == W4 && t + W4 <= kTokTile) {
+        __align__(4) cache_t four[W4];
+#pragma unroll
+        for (int k = 0; k < W4; ++k) four[k] = conv[(t + k) % kTokTile];
+        *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(four);
+      } else {
+        *dst = conv[t];
+      }
+    }
+  }
+}
+
+// grid.x = ceil(num_tokens / kTokTile), grid.y = parts the heads are split into (small
+// writes - decode steps - would otherwise occupy a handful of SMs); block = 256 threads.
+template <typename in_t, typename cache_t, int KV>
+__global__ void __launch_bounds__(256, 3)
 reshape_and_cache_kernel(const in_t* __restrict__ key, const in_t* __restrict__ value,
                          cache_t* __restrict__ key_cache, cache_t* __restrict__ value_cache,
                          const int64_t* __restrict__ slot_mapping, int64_t key_stride,
@@ -212,13 +351,18 @@ reshape_and_cache_kernel(const in_t* __restrict__ key, const in_t* __restrict__ 
   __shared__ TileSlots ts;
   const int tok0 = blockIdx.x * kTokTile;
   const int ntok = min(kTokTile, num_tokens - tok0);
-  load_tile_slots(ts, slot_mapping, tok0, ntok, block_size);
+  load_tile_slots(ts, slot_mapping, tok0, ntok, block_size, int(sizeof(cache_t)));
 
   const float k_scale_f = (KV == kKvAuto) ? 1.f : *k_scale_ptr;
   const float v_scale_f = (KV == kKvAuto) ? 1.f : *v_scale_ptr;
   const ScaledDiv k_scale(k_scale_f), v_scale(v_scale_f);
   const int chunks = head_size / x;  // per head
   const int hd = num_heads * head_size;
+  // this CTA's heads
+  const int heads_per = (num_heads + gridDim.y - 1) / gridDim.y;
+  const int h0 = blockIdx.y * heads_per;
+  const int nh = min(heads_per, num_heads - h0);
+  if (nh <= 0) return;
   // 16-byte loads from key/value rows are legal when bases and row strides are 16-byte
   // multiples; x elements = 16 bytes of cache in the standard layout
   const bool vec_ok =
@@ -228,9 +372,10 @@ reshape_and_cache_kernel(const in_t* __restrict__ key, const in_t* __restrict__ 
         (size_t(x) * sizeof(in_t))) & 15) == 0 &&
       x * int(sizeof(cache_t)) == 16 && (KV == kKvAuto || (k_scale.fast && v_scale.fast));
   if (!vec_ok) {
-    reshape_tile_generic<in_t, cache_t, KV>(ts, key, value, key_cache, value_cache, key_stride,
-                                            value_stride, tok0, ntok, num_heads, head_size,
-                                            block_size, x, k_scale_f, v_scale_f);
+    if (blockIdx.y == 0)
+      reshape_tile_generic<in_t, cache_t, KV>(ts, key, value, key_cache, value_cache, key_stride,
+                                              value_stride, tok0, ntok, num_heads, head_size,
+                                              block_size, x, k_scale_f, v_scale_f);
     return;
   }
 
@@ -240,9 +385,10 @@ reshape_and_cache_kernel(const in_t* __restrict__ key, const in_t* __restrict__ 
     constexpr int N = 16 / sizeof(cache_t);   // elements per 16-byte store
     constexpr int L = N * sizeof(in_t) / 16;  // 16-byte loads that feed it
     constexpr int KB = 4;
-    const int per_tok = num_heads * chunks;
+    const int per_tok = nh * chunks;
     const int k_items = ntok * per_tok;
     const SmallDiv by_tok(per_tok), by_chunks(chunks);
+    const int e0 = h0 * head_size;  // first element of this CTA's heads in a token row
     for (int it0 = threadIdx.x; it0 < k_items; it0 += KB * blockDim.x) {
       __align__(16) in_t in[KB][N];
       cache_t* dst[KB];
@@ -253,12 +399,14 @@ reshape_and_cache_kernel(const in_t* __restrict__ key, const in_t* __restrict__ 
         if (it < k_items) {
           const int t = int(by_tok(it));
           const int j = it - t * per_tok;
-          const int h = int(by_chunks(j));
-          const int c = j - h * chunks;
+          const int hl = int(by_chunks(j));
+          const int c = j - hl * chunks;
           const int64_t b = ts.blk[t];
           if (b >= 0) {
-            const in_t* src = key + int64_t(tok0 + t) * key_stride + j * x;  // j * x = h * head_size + c * x
-            dst[k] = key_cache + (((b * num_heads + h) * chunks + c) * int64_t(block_size) + ts.off[t]) * x;
+            // j * x = hl * head_size + c * x
+            const in_t* src = key + int64_t(tok0 + t) * key_stride + e0 + j * x;
+            dst[k] = key_cache +
+                     (((b * num_heads + h0 + hl) * chunks + c) * int64_t(block_size) + ts.off[t]) * x;
 #pragma unroll
             for (int i = 0; i < L; ++i)
               reinterpret_cast<uint4*>(in[k])[i] = reinterpret_cast<const uint4*>(src)[i];
@@ -286,9 +434,9 @@ reshape_and_cache_kernel(const in_t* __restrict__ key, const in_t* __restrict__ 
     // consecutive d of one head for the 16 tokens and writes VD rows of 16 tokens each.
     const int64_t b = ts.blk[0];
     const int off = ts.off[0];
-    const int groups = hd / VD;
+    const int groups = nh * head_size / VD;
     for (int gidx = threadIdx.x; gidx < groups; gidx += blockDim.x) {
-      const int row0 = gidx * VD;  // (head, d) flattened; a group never straddles a head
+      const int row0 = h0 * head_size + gidx * VD;  // (head, d) flattened; a group never straddles a head
       const in_t* src = value + int64_t(tok0) * value_stride + row0;
       __align__(8) in_t in[kTokTile][VD];
 #pragma unroll
@@ -296,11 +444,11 @@ reshape_and_cache_kernel(const in_t* __restrict__ key, const in_t* __restrict__ 
         *reinterpret_cast<uint2*>(in[t]) = *reinterpret_cast<const uint2*>(src + int64_t(t) * value_stride);
       __align__(16) cache_t vals[VD][kTokTile];
 #pragma unroll
-      for (int t = 0; t < kTokTile; t += 2) {
+      for (int t = 0; t < kTokTile; t += 4) {
 #pragma unroll
         for (int d = 0; d < VD; ++d) {
-          const in_t two[2] = {in[t][d], in[t + 1][d]};
-          convert_n<in_t, cache_t, KV, 2>(two, &vals[d][t], v_scale);
+          const in_t four[4] = {in[t][d], in[t + 1][d], in[t + 2][d], in[t + 3][d]};
+          convert_n<in_t, cache_t, KV, 4>(four, &vals[d][t], v_scale);
         }
       }
       cache_t* dst = value_cache + (b * hd + row0) * int64_t(block_size) + off;
@@ -316,27 +464,8 @@ reshape_and_cache_kernel(const in_t* __restrict__ key, const in_t* __restrict__ 
     return;
   }
 
-  // Ragged tile (decode steps): a thread owns one (head, d) row and writes every run of
-  // tokens that landed in consecutive slots of one block with the widest aligned store.
-  for (int row = threadIdx.x; row < hd; row += blockDim.x) {
-    const in_t* src = value + int64_t(tok0) * value_stride + row;
-    int i = 0;
-    while (i < ntok) {
-      const int64_t b = ts.blk[i];
-      if (b < 0) { ++i; continue; }
-      const int off = ts.off[i];
-      int len = 1;
-      while (i + len < ntok && ts.blk[i + len] == b && ts.off[i + len] == off + len) ++len;
-      __align__(16) cache_t vals[kTokTile];
-#pragma unroll
-      for (int k = 0; k < kTokTile; ++k)
-        if (k < len)
-          vals[k] = store_convert<in_t, cache_t, KV>(src[int64_t(i + k) * value_stride], v_scale);
-      cache_t* dst = value_cache + (b * hd + row) * int64_t(block_size) + off;
-      store_run<cache_t, kTokTile>(dst, vals, len);
-      i += len;
-    }
-  }
+  reshape_tile_v_general<in_t, cache_t, KV>(ts, value, value_cache, value_stride, tok0, ntok, h0, nh,
+                                            head_size, hd, block_size, v_scale);
 }
 
 // Flash layout ([block][slot][head][d], NHD or HND by strides): row copies.  Same tiling as
@@ -354,7 +483,7 @@ reshape_and_cache_flash_kernel(const in_t* __restrict__ key, const in_t* __restr
   __shared__ TileSlots ts;
   const int tok0 = blockIdx.x * kTokTile;
   const int ntok = min(kTokTile, num_tokens - tok0);
-  load_tile_slots(ts, slot_mapping, tok0, ntok, block_size);
+  load_tile_slots(ts, slot_mapping, tok0, ntok, block_size, int(sizeof(cache_t)));
   const float k_scale_f = (KV == kKvAuto) ? 1.f : *k_scale_ptr;
   const float v_scale_f = (KV == kKvAuto) ? 1.f : *v_scale_ptr;
   constexpr int VEC = 16 / sizeof(in_t);  // elements per 16-byte read
@@ -442,11 +571,128 @@ __global__ void convert_fp8_kernel(void* __restrict__ dst_, const void* __restri
 }
 
 // ------------------------------------------------------------------ launchers
+static int cache_sm_count() {
+  static int cache[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cache[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    cache[dev] = n;
+  }
+  return cache[dev];
+}
+
+// The staged kernel takes 16-bit key/value tensors whose rows, and the cache's 16-byte chunks,
+// are 16-byte aligned.  Returns false when the call does not qualify (the caller then uses the
+// plain kernels); otherwise launches and stores the return code in *rc.
+template <typename in_t, typename cache_t, int KV, bool kFlash>
+static bool launch_staged(const b200pa_cache_args& a, cudaStream_t stream, int* rc) {
+  if constexpr (sizeof(in_t) != 2 || sizeof(cache_t) > 2) {
+    return false;
+  } else {
+    constexpr int E = sizeof(cache_t);
+    auto al16 = [](const void* ptr) { return reinterpret_cast<uintptr_t>(ptr) % 16 == 0; };
+    const int D = a.head_size;
+    if (D % 16 != 0 || D > 512) return false;
+    if (!al16(a.key) || !al16(a.value) || !al16(a.key_cache) || !al16(a.value_cache)) return false;
+    if ((a.key_stride * 2) % 16 != 0 || (a.value_stride * 2) % 16 != 0) return false;
+    if (kFlash) {
+      if ((a.block_stride * E) % 16 != 0 || (a.page_stride * E) % 16 != 0 || (a.head_stride * E) % 16 != 0)
+        return false;
+    } else {
+      if (a.x != 16 / E || (a.block_size * E) % 4 != 0) return false;
+    }
+    StagedWriteParams p{};
+    p.key = a.key;
+    p.value = a.value;
+    p.key_cache = a.key_cache;
+    p.value_cache = a.value_cache;
+    p.slot_mapping = a.slot_mapping;
+    p.k_scale = a.k_scale;
+    p.v_scale = a.v_scale;
+    p.status = device_status_ptr();
+    if (p.status == nullptr) return false;
+    p.key_stride = a.key_stride;
+    p.value_stride = a.value_stride;
+    p.block_stride = a.block_stride;
+    p.page_stride = a.page_stride;
+    p.head_stride = a.head_stride;
+    p.num_tokens = a.num_tokens;
+    p.num_heads = a.num_heads;
+    p.head_size = D;
+    p.block_size = a.block_size;
+    p.pitch = D * 2 + 16;
+    p.stage_bytes = kStagedTile * p.pitch + 128;
+    p.nstages = 2;
+    int max_warps = kStagedMaxWarps;
+    {  // developer knobs, read once
+      static const int kn_stages = [] { const char* e = getenv("B200PA_TUNE_KVW_STAGES"); return e ? atoi(e) : 0; }();
+      static const int kn_warps = [] { const char* e = getenv("B200PA_TUNE_KVW_WARPS"); return e ? atoi(e) : 0; }();
+      if (kn_stages >= 1 && kn_stages <= 8) p.nstages = kn_stages;
+      if (kn_warps >= 4 && kn_warps <= kStagedMaxWarps) max_warps = kn_warps;
+    }
+    const size_t budget = 220 * 1024;
+    int warps = int(std::min<size_t>(max_warps, (budget - 1024) / (size_t(p.nstages) * p.stage_bytes)));
+    warps &= ~3;
+    if (warps < 4) return false;
+    const int64_t items = int64_t((a.num_tokens + kStagedTile - 1) / kStagedTile) * a.num_heads * 2;
+    // few items (decode steps): one per warp, spread over the SMs
+    const int sms = cache_sm_count();
+    const int per_cta = int(std::min<int64_t>(warps, std::max<int64_t>(4, ((items + sms - 1) / sms + 3) & ~3)));
+    const int grid = int(std::min<int64_t>(sms, (items + per_cta - 1) / per_cta));
+    const size_t smem = ((size_t(per_cta) * p.nstages * 8 + 127) & ~size_t(127)) +
+                        size_t(per_cta) * p.nstages * p.stage_bytes;
+    auto kern = kv_write_staged_kernel<in_t, cache_t, KV, kFlash>;
+    static bool done[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess && (dev < 0 || dev >= 64 || !done[dev])) {
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
+      if (e == cudaSuccess && dev >= 0 && dev < 64) done[dev] = true;
+    }
+    if (e != cudaSuccess) {
+      (void)cudaGetLastError();
+      return false;
+    }
+    kern<<<grid, per_cta * 32, smem, stream>>>(p);
+    count_launch();
+    e = cudaGetLastError();
+    if (e != cudaSuccess) {
+      set_error("KV write kernel launch failed: %s", cudaGetErrorString(e));
+      *rc = B200PA_ECUDA;
+    } else {
+      *rc = B200PA_OK;
+    }
+    return true;
+  }
+}
+
 template <typename in_t, typename cache_t, int KV>
 static int launch_reshape(const b200pa_cache_args& a, cudaStream_t stream, bool flash) {
   if (a.num_tokens == 0) return B200PA_OK;
+  // Two implementations; which one is faster was measured per case on B200 (16 384 tokens x 8
+  // heads x 128): the staged kernel for the x-layout with a 16-bit cache (31 vs 40 us), for the
+  // flash layout with an fp8 cache (28 vs 31 us) and for writes of a few thousand tokens or less
+  // (decode steps: 16 vs 19 us); the plain kernels for the x-layout with an fp8 cache (32 vs
+  // 39 us) and the flash layout with a 16-bit cache (26 vs 30 us).  B200PA_TUNE_KVW_STAGED=0/1
+  // forces one of them (for the tests that compare the two).
+  static const int kn_staged = [] { const char* e = getenv("B200PA_TUNE_KVW_STAGED"); return e ? atoi(e) : -1; }();
+  const bool fp8_cache = KV != kKvAuto;
+  const bool prefer_staged = a.num_tokens <= 4096 || (flash ? fp8_cache : !fp8_cache);
+  if (kn_staged == 1 || (kn_staged != 0 && prefer_staged)) {
+    int rc = B200PA_OK;
+    const bool took = flash ? launch_staged<in_t, cache_t, KV, true>(a, stream, &rc)
+                            : launch_staged<in_t, cache_t, KV, false>(a, stream, &rc);
+    if (took) return rc;
+  }
   if (!flash) {
-    dim3 grid((a.num_tokens + kTokTile - 1) / kTokTile);
+    // small writes (decode steps): split the heads over grid.y so that the write still spreads
+    // over the GPU (about two CTAs per SM)
+    const int tiles = (a.num_tokens + kTokTile - 1) / kTokTile;
+    const int parts = std::max(1, std::min(a.num_heads, (2 * 148 + tiles - 1) / tiles));
+    dim3 grid(tiles, parts);
     reshape_and_cache_kernel<in_t, cache_t, KV><<<grid, 256, 0, stream>>>(
         static_cast<const in_t*>(a.key), static_cast<const in_t*>(a.value),
         static_cast<cache_t*>(a.key_cache), static_cast<cache_t*>(a.value_cache), a.slot_mapping,

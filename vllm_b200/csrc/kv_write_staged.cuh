@@ -1,0 +1,295 @@
+// Staged KV write: the main path of reshape_and_cache / reshape_and_cache_flash for 16-bit
+// key/value tensors (csrc/cache_kernels.cu:225-358 of the reference).
+//
+// The write is a gather of token rows, a per-element conversion and a scatter into cache pages.
+// With plain loads every thread waits for its loads, converts and stores, and nothing else is
+// in flight meanwhile; measured on B200 that reached about half of the copy bandwidth.  Here the
+// loads are decoupled from the arithmetic:
+//   * one persistent CTA per SM; every WARP is an independent worker with a private ring of
+//     shared-memory stages and mbarriers (no CTA-wide barrier at all);
+//   * a work item is 16 consecutive tokens of one head of K, or of V: its 16 rows (head_size
+//     elements each) are fetched with one bulk async copy per row, issued by 16 lanes at once,
+//     up to `stages - 1` items ahead of the one being converted;
+//   * rows land at a pitch of row bytes + 16, which makes the two access patterns below free of
+//     bank conflicts;
+//   * K (both layouts) and V of the flash layout: a lane converts 16 bytes of output of one
+//     token - lanes run over tokens first, so a warp's stores fill whole 256-byte runs of a
+//     cache page whenever the tokens sit in consecutive slots;
+//   * V of the x-layout is a transpose ([token][d] -> [d][token in block]): a lane reads two
+//     adjacent d of all 16 tokens from shared memory, converts the two rows and writes each
+//     with one 16-byte store when the tile fills 16 aligned consecutive slots, else four bytes
+//     at a time where consecutive tokens allow it, else element by element (decode steps);
+//   * every mbarrier wait is bounded; a wait that runs out records a status code and the warp
+//     leaves.
+#pragma once
+
+#include "decode_common.cuh"
+
+namespace b200pa {
+
+struct StagedWriteParams {
+  const void* key;
+  const void* value;
+  void* key_cache;
+  void* value_cache;
+  const int64_t* slot_mapping;
+  const float* k_scale;
+  const float* v_scale;
+  int* status;
+  int64_t key_stride;    // elements
+  int64_t value_stride;
+  int64_t block_stride;  // flash layout: elements of the cache
+  int64_t page_stride;
+  int64_t head_stride;
+  int num_tokens;
+  int num_heads;
+  int head_size;
+  int block_size;
+  int nstages;
+  int pitch;        // bytes between two token rows of a stage
+  int stage_bytes;  // 16 rows + slot table
+};
+
+constexpr int kStagedTile = 16;  // tokens per work item
+constexpr int kStagedMaxWarps = 24;
+
+// 16 input elements (two 16-byte shared-memory reads) -> 16 bytes of cache, or 8 -> 16 for a
+// 16-bit cache (plain copy).
+template <typename in_t, typename cache_t, int KV>
+__device__ __forceinline__ uint4 staged_chunk(const unsigned char* src, const ScaledDiv& div) {
+  if constexpr (KV == kKvAuto) {
+    return *reinterpret_cast<const uint4*>(src);
+  } else {
+    __align__(16) in_t in[16];
+    reinterpret_cast<uint4*>(in)[0] = reinterpret_cast<const uint4*>(src)[0];
+    reinterpret_cast<uint4*>(in)[1] = reinterpret_cast<const uint4*>(src)[1];
+    __align__(16) cache_t out[16];
+    convert_n<in_t, cache_t, KV, 16>(in, out, div);
+    return *reinterpret_cast<const uint4*>(out);
+  }
+}
+
+template <typename in_t, typename cache_t, int KV, bool kFlash>
+__global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kernel(const StagedWriteParams p) {
+  static_assert(sizeof(in_t) == 2, "16-bit key/value tensors");
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  constexpr int E = sizeof(cache_t);       // 1 (fp8) or 2
+  constexpr int CH = 16 / E;               // elements per 16-byte chunk of cache (= x)
+  constexpr int CHB = CH * 2;              // bytes of input that feed one chunk
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int nwarps = blockDim.x >> 5;
+  const int D = p.head_size;
+  const int H = p.num_heads;
+  const int B = p.block_size;
+  const int NST = p.nstages;
+  const int row_bytes = D * 2;
+  const int b_shift = (B & (B - 1)) == 0 ? 31 - __clz(B) : -1;
+  const int tiles = (p.num_tokens + kStagedTile - 1) / kStagedTile;
+  const unsigned items = unsigned(tiles) * unsigned(H) * 2u;
+  const unsigned grid_warps = gridDim.x * unsigned(nwarps);
+  // items are numbered (tile, head, K or V) and dealt out SM-first
+  unsigned next_item = unsigned(warp) * gridDim.x + blockIdx.x;
+
+  // ---- shared memory: [mbarriers of all warps][stages of warp 0][stages of warp 1]...
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw);
+  const uint32_t bars_bytes = (uint32_t(nwarps) * NST * 8 + 127u) & ~127u;
+  unsigned char* my_stages = smem_raw + bars_bytes + size_t(warp) * NST * p.stage_bytes;
+  const uint32_t my_bar0 = smem_u32(bars) + uint32_t(warp) * NST * 8;
+  if (lane == 0) {
+    for (int s = 0; s < NST; ++s) mbar_init(my_bar0 + s * 8, 1);
+    fence_barrier_init();
+  }
+  __syncwarp();
+
+  const ScaledDiv k_div(KV == kKvAuto ? 1.f : *p.k_scale);
+  const ScaledDiv v_div(KV == kKvAuto ? 1.f : *p.v_scale);
+  const char* key_b = static_cast<const char*>(p.key);
+  const char* val_b = static_cast<const char*>(p.value);
+  const uint64_t policy = policy_evict_first();
+
+  // a stage: 16 rows, then the 16 slots of the tile
+  const int slot_off = kStagedTile * p.pitch;
+
+  // The slot of a token is needed before its row can be requested; it is loaded one item ahead
+  // (`slot_ahead` belongs to the item that the next produce() call will request), so that the
+  // producer never waits for that load.
+  auto load_slot = [&](unsigned item) -> int64_t {
+    if (item >= items) return -1;
+    const int tile = int((item >> 1) / unsigned(H));
+    const int tok = tile * kStagedTile + (lane & 15);
+    return tok < p.num_tokens ? p.slot_mapping[tok] : int64_t(-1);
+  };
+  int64_t slot_ahead = load_slot(next_item);
+
+  auto produce = [&](unsigned item, int stage) {
+    const bool is_v = (item & 1u) != 0;
+    const int tile = int((item >> 1) / unsigned(H));
+    const int h = int((item >> 1) - unsigned(tile) * unsigned(H));
+    const int t = lane & 15;
+    const int tok = tile * kStagedTile + t;
+    const int64_t slot = slot_ahead;
+    slot_ahead = load_slot(item + grid_warps);
+    unsigned char* st = my_stages + size_t(stage) * p.stage_bytes;
+    if (lane < kStagedTile) reinterpret_cast<int64_t*>(st + slot_off)[t] = slot;
+    const bool valid = slot >= 0 && lane < kStagedTile;
+    const unsigned vmask = __ballot_sync(0xffffffffu, valid);
+    const uint32_t bar = my_bar0 + stage * 8;
+    if (lane == 0) mbar_expect_tx(bar, uint32_t(__popc(vmask)) * uint32_t(row_bytes));
+    __syncwarp();  // the expectation is set before any copy can complete on the barrier
+    if (valid) {
+      const char* src = (is_v ? val_b : key_b) +
+                        (int64_t(tok) * (is_v ? p.value_stride : p.key_stride) + int64_t(h) * D) * 2;
+      bulk_g2s(smem_u32(st) + t * p.pitch, src, uint32_t(row_bytes), bar, policy);
+    }
+  };
+
+  // ---- fill the ring
+  int prod_stage = 0, cons_stage = 0, inflight = 0;
+  uint32_t cons_phase = 0;
+  unsigned cur_item = next_item;
+  while (inflight < NST && next_item < items) {
+    produce(next_item, prod_stage);
+    next_item += grid_warps;
+    prod_stage = prod_stage + 1 == NST ? 0 : prod_stage + 1;
+    ++inflight;
+  }
+
+  while (inflight > 0) {
+    if (!__all_sync(0xffffffffu, mbar_wait(my_bar0 + cons_stage * 8, cons_phase))) {
+      if (lane == 0) atomicExch(p.status, kStatusMbarTimeout);
+      // give the copies still in flight a bounded chance to land before the shared memory goes
+      for (int i = 1; i < inflight; ++i) {
+        cons_stage = cons_stage + 1 == NST ? 0 : cons_stage + 1;
+        if (cons_stage == 0) cons_phase ^= 1;
+        mbar_wait(my_bar0 + cons_stage * 8, cons_phase);
+      }
+      return;
+    }
+    const unsigned char* st = my_stages + size_t(cons_stage) * p.stage_bytes;
+    const bool is_v = (cur_item & 1u) != 0;
+    const int tile = int((cur_item >> 1) / unsigned(H));
+    const int h = int((cur_item >> 1) - unsigned(tile) * unsigned(H));
+    // lane t (and t + 16) knows token t's cache block and offset
+    const int64_t slot = reinterpret_cast<const int64_t*>(st + slot_off)[lane & 15];
+    const bool valid = slot >= 0;
+    // (block sizes are powers of two in practice; a 64-bit division per item otherwise)
+    const int64_t blk = !valid ? 0 : (b_shift >= 0 ? slot >> b_shift : slot / B);
+    const int off = valid ? int(slot - blk * B) : 0;
+    const unsigned vmask = __ballot_sync(0xffffffffu, valid) & 0xffffu;
+
+    if (kFlash || !is_v) {
+      // ================= K (and V of the flash layout): 16-byte chunks, tokens first
+      const int chunks = D / CH;
+      const int t = lane & 15;
+      const ScaledDiv& div = is_v ? v_div : k_div;
+      const unsigned char* rows = st + t * p.pitch;
+      unsigned char* dst;
+      int64_t cstep;  // bytes between two chunks of one token in the cache
+      if constexpr (kFlash) {
+        dst = static_cast<unsigned char*>(is_v ? p.value_cache : p.key_cache) +
+              (blk * p.block_stride + int64_t(off) * p.page_stride + int64_t(h) * p.head_stride) * E;
+        cstep = 16;
+      } else {
+        dst = static_cast<unsigned char*>(p.key_cache) +
+              (((blk * H + h) * int64_t(chunks)) * B + off) * 16;
+        cstep = int64_t(B) * 16;
+      }
+      if (valid) {
+        for (int c = lane >> 4; c < chunks; c += 2) {
+          const uint4 v = staged_chunk<in_t, cache_t, KV>(rows + c * CHB, div);
+          *reinterpret_cast<uint4*>(dst + c * cstep) = v;
+        }
+      }
+    } else {
+      // ================= V of the x-layout: transpose, two adjacent d per lane
+      const int64_t s0 = __shfl_sync(0xffffffffu, slot, 0);
+      const bool in_run = (lane >= kStagedTile) || slot == s0 + lane;
+      const bool full_run = __all_sync(0xffffffffu, in_run) && vmask == 0xffffu && s0 % kStagedTile == 0 &&
+                            B % kStagedTile == 0;
+      constexpr int W4 = 4 / E;  // tokens per 4-byte store
+      // tokens that start a 4-byte group: aligned slot, the next W4 - 1 tokens follow in the block
+      bool follows = valid;
+#pragma unroll
+      for (int k = 1; k < W4; ++k) {
+        const int64_t sk = __shfl_down_sync(0xffffffffu, slot, k);
+        follows &= ((lane & 15) + k < kStagedTile) && sk == slot + k;
+      }
+      const unsigned starts =
+          __ballot_sync(0xffffffffu, follows && (off * E) % 4 == 0 && off + W4 <= B && (B * E) % 4 == 0) & 0xffffu;
+      unsigned char* vbase = static_cast<unsigned char*>(p.value_cache);
+      const unsigned char* vrows = st;
+      // every lane runs every iteration (the stores below use warp shuffles); lanes whose pair
+      // of rows lies beyond the head size only take part in those
+      for (int d_base = 0; d_base < D; d_base += 64) {
+        const int d0 = d_base + 2 * lane;
+        const bool mine = d0 < D;
+        in_t r0[kStagedTile], r1[kStagedTile];
+#pragma unroll
+        for (int t = 0; t < kStagedTile; ++t) {
+          const uint32_t two = mine ? *reinterpret_cast<const uint32_t*>(vrows + t * p.pitch + d0 * 2) : 0u;
+          r0[t] = reinterpret_cast<const in_t*>(&two)[0];
+          r1[t] = reinterpret_cast<const in_t*>(&two)[1];
+        }
+        if (vmask != 0xffffu) {  // stale shared memory in the rows of skipped tokens
+#pragma unroll
+          for (int t = 0; t < kStagedTile; ++t)
+            if (!((vmask >> t) & 1u)) r0[t] = r1[t] = in_t(0.f);
+        }
+        __align__(16) cache_t c0[kStagedTile], c1[kStagedTile];
+        convert_n<in_t, cache_t, KV, kStagedTile>(r0, c0, v_div);
+        convert_n<in_t, cache_t, KV, kStagedTile>(r1, c1, v_div);
+        if (full_run) {
+          const int64_t b0 = b_shift >= 0 ? s0 >> b_shift : s0 / B;
+          unsigned char* dst = vbase + (((b0 * H + h) * int64_t(D) + d0) * B + int(s0 - b0 * B)) * E;
+          if (mine) {
+#pragma unroll
+            for (int w = 0; w < kStagedTile * E / 16; ++w) {
+              reinterpret_cast<uint4*>(dst)[w] = reinterpret_cast<const uint4*>(c0)[w];
+              reinterpret_cast<uint4*>(dst + int64_t(B) * E)[w] = reinterpret_cast<const uint4*>(c1)[w];
+            }
+          }
+        } else {
+          unsigned covered = 0;  // tokens written as part of an earlier group
+#pragma unroll
+          for (int t = 0; t < kStagedTile; ++t) {
+            if (!((vmask >> t) & 1u) || ((covered >> t) & 1u)) continue;  // warp-uniform
+            const int64_t bt = __shfl_sync(0xffffffffu, blk, t);
+            const int ot = __shfl_sync(0xffffffffu, off, t);
+            unsigned char* dst = vbase + (((bt * H + h) * int64_t(D) + d0) * B + ot) * E;
+            if (!mine) continue;
+            if (W4 > 1 && ((starts >> t) & 1u) && t + W4 <= kStagedTile) {
+              __align__(4) cache_t g0[W4], g1[W4];
+#pragma unroll
+              for (int k = 0; k < W4; ++k) {
+                g0[k] = c0[(t + k) % kStagedTile];
+                g1[k] = c1[(t + k) % kStagedTile];
+              }
+              *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(g0);
+              *reinterpret_cast<uint32_t*>(dst + int64_t(B) * E) = *reinterpret_cast<const uint32_t*>(g1);
+              covered |= ((1u << W4) - 1u) << t;
+            } else {
+              *reinterpret_cast<cache_t*>(dst) = c0[t];
+              *reinterpret_cast<cache_t*>(dst + int64_t(B) * E) = c1[t];
+            }
+          }
+        }
+      }
+    }
+
+    // ---- release the stage and refill it
+    __syncwarp();
+    cons_stage = cons_stage + 1 == NST ? 0 : cons_stage + 1;
+    if (cons_stage == 0) cons_phase ^= 1;
+    --inflight;
+    cur_item += grid_warps;
+    if (next_item < items) {
+      produce(next_item, prod_stage);
+      next_item += grid_warps;
+      prod_stage = prod_stage + 1 == NST ? 0 : prod_stage + 1;
+      ++inflight;
+    }
+  }
+}
+
+}  // namespace b200pa
