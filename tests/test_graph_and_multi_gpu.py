@@ -87,7 +87,9 @@ def _rank_main(rank, world, port, q):
             else:
                 got = torch.empty_like(want)
                 dist.all_gather_into_tensor(got, out)
-            ok.append(bool(torch.equal(got, want)))
+            # a shard is cut into different pieces than the whole problem (the kernel balances
+            # cache blocks per warp), so the partial sums round differently: close, not equal
+            ok.append(bool(torch.allclose(got.float(), want.float(), atol=2e-3, rtol=1e-2)))
         # tokens of every sequence per rank: partial outputs + log-sum-exps, two all-gathers, merge
         from vllm_b200 import context_parallel
         got = context_parallel.decode(Wl.shard_tokens(full, world, rank))
