@@ -194,6 +194,40 @@ __device__ __forceinline__ void convert_n(const in_t (&in)[N], cache_t* out, con
   }
 }
 
+// The same conversion for 16-bit inputs that are already in registers as 32-bit words of two
+// elements each (what 16-byte loads deliver): NW input words -> NW / 2 words of fp8 codes.  Works
+// on the words directly, so nothing is unpacked into elements and packed again.
+template <typename in_t, int KV, int NW>
+__device__ __forceinline__ void convert_words(const uint32_t (&w)[NW], uint32_t (&out)[NW / 2],
+                                              const ScaledDiv& div) {
+  static_assert(sizeof(in_t) == 2 && KV != kKvAuto && NW % 2 == 0, "16-bit inputs, fp8 cache");
+  constexpr bool kE5 = KV == kKvE5M2;
+  auto slow4 = [&](uint32_t w0, uint32_t w1) -> uint32_t {
+    const in_t* e0 = reinterpret_cast<const in_t*>(&w0);
+    const in_t* e1 = reinterpret_cast<const in_t*>(&w1);
+    return uint32_t(f32_to_fp8<kE5>(__fdiv_rn(to_f32(e0[0]), div.s))) |
+           (uint32_t(f32_to_fp8<kE5>(__fdiv_rn(to_f32(e0[1]), div.s))) << 8) |
+           (uint32_t(f32_to_fp8<kE5>(__fdiv_rn(to_f32(e1[0]), div.s))) << 16) |
+           (uint32_t(f32_to_fp8<kE5>(__fdiv_rn(to_f32(e1[1]), div.s))) << 24);
+  };
+  if (!div.fast) {  // the same for every thread of the launch
+#pragma unroll
+    for (int i = 0; i < NW; i += 2) out[i / 2] = slow4(w[i], w[i + 1]);
+    return;
+  }
+  uint32_t nan_bits = 0;
+#pragma unroll
+  for (int i = 0; i < NW; i += 2) {
+    const uint32_t v = neg_quant4<in_t, kE5>(w[i], w[i + 1], div);
+    nan_bits |= (v & 0x7F7F7F7Fu) + 0x01010101u;  // bit 7 of a byte: its low seven bits were all ones
+    out[i / 2] = v ^ 0x80808080u;
+  }
+  if ((nan_bits & 0x80808080u) != 0) {
+#pragma unroll
+    for (int i = 0; i < NW; i += 2) out[i / 2] = slow4(w[i], w[i + 1]);
+  }
+}
+
 }  // namespace b200pa
 
 #include "kv_write_staged.cuh"
@@ -416,9 +450,17 @@ reshape_and_cache_kernel(const in_t* __restrict__ key, const in_t* __restrict__ 
 #pragma unroll
       for (int k = 0; k < KB; ++k) {
         if (dst[k] != nullptr) {
-          __align__(16) cache_t vals[N];
-          convert_n<in_t, cache_t, KV, N>(in[k], vals, k_scale);
-          *reinterpret_cast<uint4*>(dst[k]) = *reinterpret_cast<const uint4*>(vals);
+          if constexpr (KV != kKvAuto && sizeof(in_t) == 2) {
+            uint32_t wi[8], wo[4];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) wi[i] = reinterpret_cast<const uint32_t*>(in[k])[i];
+            convert_words<in_t, KV, 8>(wi, wo, k_scale);
+            *reinterpret_cast<uint4*>(dst[k]) = make_uint4(wo[0], wo[1], wo[2], wo[3]);
+          } else {
+            __align__(16) cache_t vals[N];
+            convert_n<in_t, cache_t, KV, N>(in[k], vals, k_scale);
+            *reinterpret_cast<uint4*>(dst[k]) = *reinterpret_cast<const uint4*>(vals);
+          }
         }
       }
     }
@@ -443,12 +485,30 @@ reshape_and_cache_kernel(const in_t* __restrict__ key, const in_t* __restrict__ 
       for (int t = 0; t < kTokTile; ++t)
         *reinterpret_cast<uint2*>(in[t]) = *reinterpret_cast<const uint2*>(src + int64_t(t) * value_stride);
       __align__(16) cache_t vals[VD][kTokTile];
-#pragma unroll
-      for (int t = 0; t < kTokTile; t += 4) {
+      if constexpr (KV != kKvAuto && sizeof(in_t) == 2) {
+        // token t's 8 bytes are two words: (d0, d1) and (d2, d3).  The cache row of d0 needs the
+        // low halves of the first words of consecutive tokens, d1 the high halves, and so on: one
+        // byte permute per pair of tokens.
 #pragma unroll
         for (int d = 0; d < VD; ++d) {
-          const in_t four[4] = {in[t][d], in[t + 1][d], in[t + 2][d], in[t + 3][d]};
-          convert_n<in_t, cache_t, KV, 4>(four, &vals[d][t], v_scale);
+          const uint32_t sel = (d & 1) ? 0x7632u : 0x5410u;
+          uint32_t wi[kTokTile / 2], wo[kTokTile / 4];
+#pragma unroll
+          for (int t = 0; t < kTokTile; t += 2)
+            wi[t / 2] = __byte_perm(reinterpret_cast<const uint32_t*>(in[t])[d >> 1],
+                                    reinterpret_cast<const uint32_t*>(in[t + 1])[d >> 1], sel);
+          convert_words<in_t, KV, kTokTile / 2>(wi, wo, v_scale);
+#pragma unroll
+          for (int i = 0; i < kTokTile / 4; ++i) reinterpret_cast<uint32_t*>(vals[d])[i] = wo[i];
+        }
+      } else {
+#pragma unroll
+        for (int t = 0; t < kTokTile; t += 4) {
+#pragma unroll
+          for (int d = 0; d < VD; ++d) {
+            const in_t four[4] = {in[t][d], in[t + 1][d], in[t + 2][d], in[t + 3][d]};
+            convert_n<in_t, cache_t, KV, 4>(four, &vals[d][t], v_scale);
+          }
         }
       }
       cache_t* dst = value_cache + (b * hd + row0) * int64_t(block_size) + off;
@@ -525,7 +585,16 @@ reshape_and_cache_flash_kernel(const in_t* __restrict__ key, const in_t* __restr
         for (int k = 0; k < KB; ++k) {
           if (dst[k] != nullptr) {
             __align__(16) cache_t outv[VEC];
-            convert_n<in_t, cache_t, KV, VEC>(in[k], outv, scale);
+            if constexpr (KV != kKvAuto && sizeof(in_t) == 2) {
+              uint32_t wi[4], wo[2];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) wi[i] = reinterpret_cast<const uint32_t*>(in[k])[i];
+              convert_words<in_t, KV, 4>(wi, wo, scale);
+              reinterpret_cast<uint32_t*>(outv)[0] = wo[0];
+              reinterpret_cast<uint32_t*>(outv)[1] = wo[1];
+            } else {
+              convert_n<in_t, cache_t, KV, VEC>(in[k], outv, scale);
+            }
             if constexpr (sizeof(cache_t) * VEC == 16) {
               *reinterpret_cast<uint4*>(dst[k]) = *reinterpret_cast<const uint4*>(outv);
             } else if constexpr (sizeof(cache_t) * VEC == 8) {
@@ -673,14 +742,13 @@ template <typename in_t, typename cache_t, int KV>
 static int launch_reshape(const b200pa_cache_args& a, cudaStream_t stream, bool flash) {
   if (a.num_tokens == 0) return B200PA_OK;
   // Two implementations; which one is faster was measured per case on B200 (16 384 tokens x 8
-  // heads x 128): the staged kernel for the x-layout with a 16-bit cache (31 vs 40 us), for the
-  // flash layout with an fp8 cache (28 vs 31 us) and for writes of a few thousand tokens or less
-  // (decode steps: 16 vs 19 us); the plain kernels for the x-layout with an fp8 cache (32 vs
-  // 39 us) and the flash layout with a 16-bit cache (26 vs 30 us).  B200PA_TUNE_KVW_STAGED=0/1
-  // forces one of them (for the tests that compare the two).
+  // heads x 128, us, staged / plain): x-layout fp8 32 / 31, flash fp8 27 / 29, x-layout 16-bit
+  // cache 30 / 40, 256 scattered tokens (a decode step) 14 / 17, x-layout fp8 with sequences
+  // that do not start on a tile boundary 58 / 92 - and flash with a 16-bit cache 30 / 25, the
+  // one case that stays with the plain kernel.  B200PA_TUNE_KVW_STAGED=0/1 forces one of them
+  // (for the tests that compare the two).
   static const int kn_staged = [] { const char* e = getenv("B200PA_TUNE_KVW_STAGED"); return e ? atoi(e) : -1; }();
-  const bool fp8_cache = KV != kKvAuto;
-  const bool prefer_staged = a.num_tokens <= 4096 || (flash ? fp8_cache : !fp8_cache);
+  const bool prefer_staged = !(flash && KV == kKvAuto) || a.num_tokens <= 4096;
   if (kn_staged == 1 || (kn_staged != 0 && prefer_staged)) {
     int rc = B200PA_OK;
     const bool took = flash ? launch_staged<in_t, cache_t, KV, true>(a, stream, &rc)

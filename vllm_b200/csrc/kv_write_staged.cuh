@@ -60,12 +60,12 @@ __device__ __forceinline__ uint4 staged_chunk(const unsigned char* src, const Sc
   if constexpr (KV == kKvAuto) {
     return *reinterpret_cast<const uint4*>(src);
   } else {
-    __align__(16) in_t in[16];
-    reinterpret_cast<uint4*>(in)[0] = reinterpret_cast<const uint4*>(src)[0];
-    reinterpret_cast<uint4*>(in)[1] = reinterpret_cast<const uint4*>(src)[1];
-    __align__(16) cache_t out[16];
-    convert_n<in_t, cache_t, KV, 16>(in, out, div);
-    return *reinterpret_cast<const uint4*>(out);
+    const uint4 a = reinterpret_cast<const uint4*>(src)[0];
+    const uint4 b = reinterpret_cast<const uint4*>(src)[1];
+    const uint32_t wi[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    uint32_t wo[4];
+    convert_words<in_t, KV, 8>(wi, wo, div);
+    return make_uint4(wo[0], wo[1], wo[2], wo[3]);
   }
 }
 
@@ -102,8 +102,6 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
   }
   __syncwarp();
 
-  const ScaledDiv k_div(KV == kKvAuto ? 1.f : *p.k_scale);
-  const ScaledDiv v_div(KV == kKvAuto ? 1.f : *p.v_scale);
   const char* key_b = static_cast<const char*>(p.key);
   const char* val_b = static_cast<const char*>(p.value);
   const uint64_t policy = policy_evict_first();
@@ -111,16 +109,21 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
   // a stage: 16 rows, then the 16 slots of the tile
   const int slot_off = kStagedTile * p.pitch;
 
-  // The slot of a token is needed before its row can be requested; it is loaded one item ahead
-  // (`slot_ahead` belongs to the item that the next produce() call will request), so that the
-  // producer never waits for that load.
+  // The slot of a token is needed before its row can be requested; it is loaded two items ahead
+  // (`slot_a` belongs to the item that the next produce() call will request, `slot_b` to the one
+  // after), so that the producer never waits for that load.  The load is a volatile asm
+  // statement: the compiler would otherwise move it down to its use.
   auto load_slot = [&](unsigned item) -> int64_t {
     if (item >= items) return -1;
     const int tile = int((item >> 1) / unsigned(H));
     const int tok = tile * kStagedTile + (lane & 15);
-    return tok < p.num_tokens ? p.slot_mapping[tok] : int64_t(-1);
+    if (tok >= p.num_tokens) return -1;
+    int64_t v;
+    asm volatile("ld.global.nc.s64 %0, [%1];" : "=l"(v) : "l"(p.slot_mapping + tok));
+    return v;
   };
-  int64_t slot_ahead = load_slot(next_item);
+  int64_t slot_a = load_slot(next_item);
+  int64_t slot_b = load_slot(next_item + grid_warps);
 
   auto produce = [&](unsigned item, int stage) {
     const bool is_v = (item & 1u) != 0;
@@ -128,8 +131,9 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
     const int h = int((item >> 1) - unsigned(tile) * unsigned(H));
     const int t = lane & 15;
     const int tok = tile * kStagedTile + t;
-    const int64_t slot = slot_ahead;
-    slot_ahead = load_slot(item + grid_warps);
+    const int64_t slot = slot_a;
+    slot_a = slot_b;
+    slot_b = load_slot(item + 2 * grid_warps);
     unsigned char* st = my_stages + size_t(stage) * p.stage_bytes;
     if (lane < kStagedTile) reinterpret_cast<int64_t*>(st + slot_off)[t] = slot;
     const bool valid = slot >= 0 && lane < kStagedTile;
@@ -154,6 +158,11 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
     prod_stage = prod_stage + 1 == NST ? 0 : prod_stage + 1;
     ++inflight;
   }
+
+  // (the scales are read after the first rows have been requested: their latency hides behind
+  // the copies)
+  const ScaledDiv k_div(KV == kKvAuto ? 1.f : *p.k_scale);
+  const ScaledDiv v_div(KV == kKvAuto ? 1.f : *p.v_scale);
 
   while (inflight > 0) {
     if (!__all_sync(0xffffffffu, mbar_wait(my_bar0 + cons_stage * 8, cons_phase))) {
@@ -224,21 +233,38 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
       for (int d_base = 0; d_base < D; d_base += 64) {
         const int d0 = d_base + 2 * lane;
         const bool mine = d0 < D;
-        in_t r0[kStagedTile], r1[kStagedTile];
+        uint32_t two[kStagedTile];  // token t: (d0, d0 + 1)
 #pragma unroll
-        for (int t = 0; t < kStagedTile; ++t) {
-          const uint32_t two = mine ? *reinterpret_cast<const uint32_t*>(vrows + t * p.pitch + d0 * 2) : 0u;
-          r0[t] = reinterpret_cast<const in_t*>(&two)[0];
-          r1[t] = reinterpret_cast<const in_t*>(&two)[1];
-        }
+        for (int t = 0; t < kStagedTile; ++t)
+          two[t] = mine ? *reinterpret_cast<const uint32_t*>(vrows + t * p.pitch + d0 * 2) : 0u;
         if (vmask != 0xffffu) {  // stale shared memory in the rows of skipped tokens
 #pragma unroll
           for (int t = 0; t < kStagedTile; ++t)
-            if (!((vmask >> t) & 1u)) r0[t] = r1[t] = in_t(0.f);
+            if (!((vmask >> t) & 1u)) two[t] = 0u;
         }
         __align__(16) cache_t c0[kStagedTile], c1[kStagedTile];
-        convert_n<in_t, cache_t, KV, kStagedTile>(r0, c0, v_div);
-        convert_n<in_t, cache_t, KV, kStagedTile>(r1, c1, v_div);
+        if constexpr (KV != kKvAuto) {
+          // row d0 takes the low halves of consecutive tokens' words, row d0 + 1 the high halves
+          uint32_t w0[kStagedTile / 2], w1[kStagedTile / 2], o0[kStagedTile / 4], o1[kStagedTile / 4];
+#pragma unroll
+          for (int t = 0; t < kStagedTile; t += 2) {
+            w0[t / 2] = __byte_perm(two[t], two[t + 1], 0x5410u);
+            w1[t / 2] = __byte_perm(two[t], two[t + 1], 0x7632u);
+          }
+          convert_words<in_t, KV, kStagedTile / 2>(w0, o0, v_div);
+          convert_words<in_t, KV, kStagedTile / 2>(w1, o1, v_div);
+#pragma unroll
+          for (int i = 0; i < kStagedTile / 4; ++i) {
+            reinterpret_cast<uint32_t*>(c0)[i] = o0[i];
+            reinterpret_cast<uint32_t*>(c1)[i] = o1[i];
+          }
+        } else {
+#pragma unroll
+          for (int t = 0; t < kStagedTile; t += 2) {
+            reinterpret_cast<uint32_t*>(c0)[t / 2] = __byte_perm(two[t], two[t + 1], 0x5410u);
+            reinterpret_cast<uint32_t*>(c1)[t / 2] = __byte_perm(two[t], two[t + 1], 0x7632u);
+          }
+        }
         if (full_run) {
           const int64_t b0 = b_shift >= 0 ? s0 >> b_shift : s0 / B;
           unsigned char* dst = vbase + (((b0 * H + h) * int64_t(D) + d0) * B + int(s0 - b0 * B)) * E;
