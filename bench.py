@@ -178,7 +178,7 @@ def read_peak_gbs(dev) -> float:
 
 
 def build_workload(name: str, device, world: int, rank: int, num_seqs=None):
-    from vllm_b200 import workloads as W
+    import workloads as W
 
     if num_seqs is not None:
         if name == "cfg2":
@@ -281,7 +281,7 @@ def ref_gpu_ops():
 
 def attention_case(w, version: str, steps: int, warmup: int, peaks, with_ref: bool = True):
     """Times one attention configuration (and the reference CUDA kernel on the same tensors)."""
-    from vllm_b200 import workloads as W
+    import workloads as W
 
     dev = w.query.device
     scratch = w.scratch() if version == "v2" else None
@@ -371,7 +371,7 @@ def _free():
 
 def extra_configs(dev, peaks, steps: int = 30, warmup: int = 5):
     """The benchmark configurations besides the headline one, on one GPU."""
-    from vllm_b200 import workloads as W
+    import workloads as W
 
     out = {}
     w = W.config1(dev)
@@ -403,7 +403,7 @@ def strong_scaling(dev, world: int, rank: int, peaks, td, steps: int = 30, warmu
     sequences with a private block pool for the large-batch one); rank 0 also times the whole
     problem on its GPU.  No collective on the data path; after the timed region the shards'
     outputs are all-gathered over NCCL and compared with the unsharded result on rank 0."""
-    from vllm_b200 import workloads as W
+    import workloads as W
 
     assert world > 1
     res = {}
@@ -522,7 +522,7 @@ def main() -> int:
 
     from vllm_b200 import _custom_ops as ops  # noqa: F401  (fails loudly if the .so is missing)
     from vllm_b200 import capi
-    from vllm_b200 import workloads as W
+    import workloads as W
 
     is_write = version in ("cfg3w", "cfg3wf")
     if is_write:

@@ -129,7 +129,7 @@ def test_convert_fp8_round_trip():
 
 def test_write_then_attend_uses_the_written_tokens():
     """reshape_and_cache -> paged_attention_v2 on the same cache (the decode step)."""
-    from vllm_b200 import workloads as W
+    import workloads as W
     w = W.config3(DEV, num_seqs=4, seq_len=1024, new_tokens=128)
     ops.reshape_and_cache(w.new_key, w.new_value, w.key_cache, w.value_cache, w.slot_mapping, "fp8",
                           w.k_scale, w.v_scale)

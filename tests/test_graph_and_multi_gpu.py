@@ -11,7 +11,7 @@ import pytest
 import torch
 
 from vllm_b200 import _custom_ops as ops
-from vllm_b200 import workloads as W
+import workloads as W
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parents[1]
@@ -71,7 +71,7 @@ def _rank_main(rank, world, port, q):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
-        from vllm_b200 import workloads as Wl
+        import workloads as Wl
         full = Wl.small(dev, seed=51, num_seqs=8, num_heads=32, num_kv_heads=8, max_len=2500, num_blocks=2048)
         full.query.mul_(10.0)
         want = Wl.run_attention(full, version="v2")

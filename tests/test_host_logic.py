@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from vllm_b200 import _custom_ops as ops
-from vllm_b200 import workloads as W
+import workloads as W
 from vllm_b200.paged_attn import PagedAttention, _PARTITION_SIZE
 
 
@@ -122,7 +122,7 @@ def test_token_ranges_cover_every_token_once_at_block_boundaries():
     """Token sharding plan (decode context parallelism): the ranks' ranges of a sequence are
     block-aligned, contiguous, disjoint and together cover it; the ragged tail goes to one rank."""
     import numpy as np
-    from vllm_b200 import workloads as W
+    import workloads as W
 
     lens = np.array([0, 1, 15, 16, 17, 700, 4096, 4097, 33])
     for block_size in (16, 32):

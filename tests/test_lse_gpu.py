@@ -9,7 +9,7 @@ import torch
 from oracle import paged_oracle as O
 from vllm_b200 import _custom_ops as ops
 from vllm_b200 import capi, context_parallel
-from vllm_b200 import workloads as W
+import workloads as W
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"

@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from vllm_b200 import _custom_ops
-from vllm_b200 import workloads as W
+import workloads as W
 
 pytestmark = pytest.mark.gpu
 _custom_ops.claim_reference_names()  # the checks below address the ops by the reference's names

@@ -35,7 +35,7 @@ def _worker(rank, world, port, q):
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        from vllm_b200 import workloads as W
+        import workloads as W
         # every rank derives the same full plan from the same seed
         full = W.small("cpu", seed=21, num_seqs=6, num_heads=8, num_kv_heads=4, head_size=64,
                        max_len=700, num_blocks=256)
