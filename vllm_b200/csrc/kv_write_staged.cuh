@@ -234,9 +234,15 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
         const int d0 = d_base + 2 * lane;
         const bool mine = d0 < D;
         uint32_t two[kStagedTile];  // token t: (d0, d0 + 1)
+        if (mine) {
+          const unsigned char* col = vrows + d0 * 2;
+          const int pitch = p.pitch;
 #pragma unroll
-        for (int t = 0; t < kStagedTile; ++t)
-          two[t] = mine ? *reinterpret_cast<const uint32_t*>(vrows + t * p.pitch + d0 * 2) : 0u;
+          for (int t = 0; t < kStagedTile; ++t) two[t] = *reinterpret_cast<const uint32_t*>(col + t * pitch);
+        } else {
+#pragma unroll
+          for (int t = 0; t < kStagedTile; ++t) two[t] = 0u;
+        }
         if (vmask != 0xffffu) {  // stale shared memory in the rows of skipped tokens
 #pragma unroll
           for (int t = 0; t < kStagedTile; ++t)
