@@ -86,9 +86,12 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
   const int row_bytes = D * 2;
   const int b_shift = (B & (B - 1)) == 0 ? 31 - __clz(B) : -1;
   const int tiles = (p.num_tokens + kStagedTile - 1) / kStagedTile;
-  const unsigned items = unsigned(tiles) * unsigned(H) * 2u;
+  // Items: the (tile, head) pairs of K, then those of V, dealt out SM-first.  Every warp walks
+  // through both halves, so the K and V work (which differ in cost in the x-layout) is spread
+  // evenly over warps and SMs.
+  const unsigned pairs = unsigned(tiles) * unsigned(H);
+  const unsigned items = pairs * 2u;
   const unsigned grid_warps = gridDim.x * unsigned(nwarps);
-  // items are numbered (tile, head, K or V) and dealt out SM-first
   unsigned next_item = unsigned(warp) * gridDim.x + blockIdx.x;
 
   // ---- shared memory: [mbarriers of all warps][stages of warp 0][stages of warp 1]...
@@ -115,7 +118,7 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
   // statement: the compiler would otherwise move it down to its use.
   auto load_slot = [&](unsigned item) -> int64_t {
     if (item >= items) return -1;
-    const int tile = int((item >> 1) / unsigned(H));
+    const int tile = int((item >= pairs ? item - pairs : item) / unsigned(H));
     const int tok = tile * kStagedTile + (lane & 15);
     if (tok >= p.num_tokens) return -1;
     int64_t v;
@@ -126,9 +129,10 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
   int64_t slot_b = load_slot(next_item + grid_warps);
 
   auto produce = [&](unsigned item, int stage) {
-    const bool is_v = (item & 1u) != 0;
-    const int tile = int((item >> 1) / unsigned(H));
-    const int h = int((item >> 1) - unsigned(tile) * unsigned(H));
+    const bool is_v = item >= pairs;
+    const unsigned pr = is_v ? item - pairs : item;
+    const int tile = int(pr / unsigned(H));
+    const int h = int(pr - unsigned(tile) * unsigned(H));
     const int t = lane & 15;
     const int tok = tile * kStagedTile + t;
     const int64_t slot = slot_a;
@@ -176,9 +180,9 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
       return;
     }
     const unsigned char* st = my_stages + size_t(cons_stage) * p.stage_bytes;
-    const bool is_v = (cur_item & 1u) != 0;
-    const int tile = int((cur_item >> 1) / unsigned(H));
-    const int h = int((cur_item >> 1) - unsigned(tile) * unsigned(H));
+    const bool is_v = cur_item >= pairs;
+    const unsigned cur_pr = is_v ? cur_item - pairs : cur_item;
+    const int h = int(cur_pr % unsigned(H));
     // lane t (and t + 16) knows token t's cache block and offset
     const int64_t slot = reinterpret_cast<const int64_t*>(st + slot_off)[lane & 15];
     const bool valid = slot >= 0;
