@@ -316,10 +316,12 @@ def attention_case(w, version: str, steps: int, warmup: int, peaks, with_ref: bo
     return res
 
 
-def write_case(w, layout: str, kv: str, steps: int, warmup: int, peaks, tokens=None):
+def write_case(w, layout: str, kv: str, steps: int, warmup: int, peaks, tokens=None, shift: int = 0):
     """Times the KV write of config 3's shape: `layout` x|flash, cache type `kv` fp8|auto,
     `tokens` = None for the prefill-shaped write (128 new tokens per sequence, consecutive
-    slots) or a count for a decode-shaped one (that many scattered slots, one per sequence)."""
+    slots) or a count for a decode-shaped one (that many scattered slots, one per sequence);
+    `shift` moves every slot down by that many positions, so that the 16-token tiles of the
+    prefill-shaped write straddle cache blocks (sequences that do not start on a block edge)."""
     from vllm_b200 import _custom_ops as ops
 
     dev = w.query.device
@@ -331,6 +333,8 @@ def write_case(w, layout: str, kv: str, steps: int, warmup: int, peaks, tokens=N
         reps = (tokens + w.num_seqs - 1) // w.num_seqs
         pick = pick.repeat(reps)[:tokens]
         nk, nv, sm = nk[pick].contiguous(), nv[pick].contiguous(), sm[pick].contiguous()
+    if shift:
+        sm = sm - shift
     T = nk.shape[0]
     nb, B, H, D = w.key_cache.shape[0], w.block_size, w.num_kv_heads, w.head_size
     cdt = torch.uint8 if kv == "fp8" else nk.dtype
@@ -383,7 +387,11 @@ def extra_configs(dev, peaks, steps: int = 30, warmup: int = 5):
     out["cfg3w"] = write_case(w, "x", "fp8", steps, warmup, peaks)
     out["cfg3wf"] = write_case(w, "flash", "fp8", steps, warmup, peaks)
     out["cfg3w_auto"] = write_case(w, "x", "auto", steps, warmup, peaks)
+    out["cfg3wf_auto"] = write_case(w, "flash", "auto", steps, warmup, peaks)
     out["cfg3w_decode"] = write_case(w, "x", "fp8", steps, warmup, peaks, tokens=256)
+    out["cfg3w_decode1024"] = write_case(w, "x", "fp8", steps, warmup, peaks, tokens=1024)
+    out["cfg3w_shifted"] = write_case(w, "x", "fp8", steps, warmup, peaks, shift=5)
+    out["cfg3w_auto_shifted"] = write_case(w, "x", "auto", steps, warmup, peaks, shift=5)
     del w
     _free()
     w = W.config4(dev)
