@@ -10,7 +10,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
 // Status codes written to the device status word.
-enum : int { kStatusOk = 0, kStatusMbarTimeout = 1, kStatusNoRing = 2 };
+enum : int { kStatusOk = 0, kStatusMbarTimeout = 1, kStatusNoRing = 2, kStatusMergeNotes = 3 };
 
 struct DecodeParams {
   void* out;

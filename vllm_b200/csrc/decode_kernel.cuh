@@ -101,10 +101,10 @@ constexpr int kMergeDirectMax = 16;
 //   group == true (pstride 1, 2 <= np <= 32): the same sum with w_j = l_j 2^(m_j-M) / sum goes
 //     into partial 0's slot of tmp (outp points there) and (M, sum) into its statistics, so that
 //     the slot again holds a partial in the format above.
-// Overwrites exp_sums with the weights.  Kept out of line: it runs once per sequence and kv head
-// and must not cost the page loop any registers.
+// This is the general form (any number of partials and heads): the weights go through memory
+// (it overwrites exp_sums with them), three dependent round trips.
 template <typename QT, int D>
-__device__ __noinline__ void merge_partials(float* exp_sums, float* max_logits, const QT* tmp,
+__device__ __noinline__ void merge_partials_general(float* exp_sums, float* max_logits, const QT* tmp,
                                             QT* outp, int64_t out_head_stride, int64_t row0, int np,
                                             int P, int pstride, int nheads, int lane, float* lse,
                                             int lse_stride, bool group) {
@@ -256,6 +256,155 @@ __device__ __noinline__ void merge_partials(float* exp_sums, float* max_logits, 
   }
 }
 
+// Up to 32 partials of up to 4 heads (64 output units) in ONE memory round trip: the statistics
+// and the first partials are requested together, the weights stay in registers (lane j holds
+// those of partial j) and reach the lanes that accumulate by shuffle instead of through memory.
+// A lane owns two 16-byte output units; JB = partials requested per round trip.
+template <typename QT, int D, int JB>
+__device__ __noinline__ void merge_partials_fast(float* exp_sums, float* max_logits, const QT* tmp,
+                                                    QT* outp, int64_t out_head_stride, int64_t row0,
+                                                    int np, int P, int pstride, int nh, int lane,
+                                                    float* lse, int lse_stride, bool group) {
+  constexpr bool kOutBf = std::is_same_v<QT, __nv_bfloat16>;
+  constexpr int NU = 2;
+  constexpr int UPH = D / 8;  // units per head
+  const int units = nh * UPH;
+  const int64_t jstep = int64_t(pstride) * D;
+  // ---- requests: statistics of partial `lane` for the nh heads ...
+  float ml0[4], es0[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const bool ok = k < nh && lane < np;
+    const int64_t at = row0 + int64_t(ok ? k : 0) * P + int64_t(ok ? lane : 0) * pstride;
+    ml0[k] = ok ? __ldcg(max_logits + at) : -INFINITY;
+    es0[k] = ok ? __ldcg(exp_sums + at) : 0.f;
+  }
+  // ... and the first JB partials of this lane's units
+  int hl[NU];
+  bool uok[NU];
+  const QT* src[NU];
+  QT* dst[NU];
+#pragma unroll
+  for (int k2 = 0; k2 < NU; ++k2) {
+    const int u = lane + 32 * k2;
+    uok[k2] = u < units;
+    const int uu = uok[k2] ? u : 0;
+    hl[k2] = uu / UPH;
+    const int e0 = (uu % UPH) * 8;
+    src[k2] = tmp + (row0 + int64_t(hl[k2]) * P) * D + e0;
+    dst[k2] = outp + hl[k2] * out_head_stride + e0;
+  }
+  uint4 v[NU][JB];
+  auto request = [&](int jb) {
+#pragma unroll
+    for (int jj = 0; jj < JB; ++jj)
+#pragma unroll
+      for (int k2 = 0; k2 < NU; ++k2)
+        if (jb + jj < np && uok[k2])
+          v[k2][jj] = __ldcg(reinterpret_cast<const uint4*>(src[k2] + int64_t(jb + jj) * jstep));
+  };
+  request(0);
+  // ---- weights (registers): lane j holds w_j / sum of each head
+  float wn[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    float mx = ml0[k];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const float w = (k < nh && lane < np) ? es0[k] * fast_exp2(ml0[k] - mx) : 0.f;
+    float sum = w;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    wn[k] = w * __fdividef(1.f, group ? sum : sum + 1e-6f);
+    if (k < nh && lane == 0) {
+      if (group) {
+        // every lane has its statistics in registers: partial 0's slots take the merged ones
+        max_logits[row0 + int64_t(k) * P] = mx;
+        exp_sums[row0 + int64_t(k) * P] = sum;
+      } else if (lse != nullptr) {
+        lse[int64_t(k) * lse_stride] = (mx + log2f(sum)) * kLn2;
+      }
+    }
+  }
+  // ---- weighted sum
+  float acc[NU][8];
+#pragma unroll
+  for (int k2 = 0; k2 < NU; ++k2)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[k2][i] = 0.f;
+  for (int jb = 0; jb < np; jb += JB) {
+    if (jb > 0) request(jb);
+#pragma unroll
+    for (int jj = 0; jj < JB; ++jj) {
+      const int j = jb + jj;
+      if (j >= np) break;  // warp-uniform
+      const float s0 = __shfl_sync(0xffffffffu, wn[0], j);
+      const float s1 = __shfl_sync(0xffffffffu, wn[1], j);
+      const float s2 = __shfl_sync(0xffffffffu, wn[2], j);
+      const float s3 = __shfl_sync(0xffffffffu, wn[3], j);
+#pragma unroll
+      for (int k2 = 0; k2 < NU; ++k2) {
+        if (!uok[k2]) continue;
+        const float w = hl[k2] == 0 ? s0 : (hl[k2] == 1 ? s1 : (hl[k2] == 2 ? s2 : s3));
+        const uint32_t vv[4] = {v[k2][jj].x, v[k2][jj].y, v[k2][jj].z, v[k2][jj].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float f0, f1;
+          if constexpr (kOutBf) {
+            f0 = __uint_as_float(vv[i] << 16);
+            f1 = __uint_as_float(vv[i] & 0xffff0000u);
+          } else {
+            const __half2 h = *reinterpret_cast<const __half2*>(&vv[i]);
+            f0 = __low2float(h);
+            f1 = __high2float(h);
+          }
+          acc[k2][2 * i] += w * f0;
+          acc[k2][2 * i + 1] += w * f1;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int k2 = 0; k2 < NU; ++k2) {
+    if (!uok[k2]) continue;
+    uint4 o4;
+    o4.x = pack2<kOutBf>(acc[k2][0], acc[k2][1]);
+    o4.y = pack2<kOutBf>(acc[k2][2], acc[k2][3]);
+    o4.z = pack2<kOutBf>(acc[k2][4], acc[k2][5]);
+    o4.w = pack2<kOutBf>(acc[k2][6], acc[k2][7]);
+    *reinterpret_cast<uint4*>(dst[k2]) = o4;
+  }
+}
+
+// The merge of one (sequence, kv head, head group).  Both forms are out of line, each with its
+// own register frame, and called after the page loop only (a call from inside it made the
+// compiler spill the loop's state around the call).
+template <typename QT, int D>
+__device__ __forceinline__ void merge_partials(float* exp_sums, float* max_logits, const QT* tmp,
+                                            QT* outp, int64_t out_head_stride, int64_t row0, int np,
+                                            int P, int pstride, int nheads, int lane, float* lse,
+                                            int lse_stride, bool group) {
+  constexpr int UPH = D / 8;
+  constexpr int HB = UPH <= 16 ? 4 : 2;  // heads per pass: at most 64 output units
+  // Measured on B200: with more than 32 output units (three or more heads of 128) the form that
+  // requests statistics and partials together is faster (an 8-way kv-head shard of a
+  // long-context batch 65 -> 60.5 us); with fewer, where the general form lets several lanes
+  // share a unit, it is slower (MHA decode of 8 sequences 25.6 -> 27.4 us).  Four partials per
+  // round trip: with eight the function needs so many registers that the compiler spills in
+  // the kernel around the call, and the launch with few heads pays for it (29 us).
+  if (np > 32 || nheads * UPH <= 32) {
+    merge_partials_general<QT, D>(exp_sums, max_logits, tmp, outp, out_head_stride, row0, np, P, pstride,
+                                  nheads, lane, lse, lse_stride, group);
+    return;
+  }
+  for (int h0 = 0; h0 < nheads; h0 += HB) {
+    const int nh = min(HB, nheads - h0);
+    float* lse_h = lse ? lse + int64_t(h0) * lse_stride : nullptr;
+    merge_partials_fast<QT, D, 4>(exp_sums, max_logits, tmp, outp + h0 * out_head_stride, out_head_stride,
+                                  row0 + int64_t(h0) * P, np, P, pstride, nh, lane, lse_h, lse_stride, group);
+  }
+}
+
 template <typename QT, int KV, int D, int GP, int BT, int MAXW>
 __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodeParams p) {
   using TR = DecodeTraits<QT, KV, D, GP>;
@@ -302,6 +451,8 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
   // of the grid takes units [r*C, (r+1)*C).
   __shared__ int s_plan[4];      // [0] C: units per range, [1] units of one head, [2] ranges
   __shared__ int4 s_iter[MAXW];  // per warp: units left, block offset, sequence, head
+  __shared__ int4 s_todo[MAXW][2];  // per warp: merges owed (sequence, head item, pieces, piece | level)
+  __shared__ int s_ntodo[MAXW];
   const bool flat = p.use_table != 0;
   const int hsubs = p.num_kv_heads * p.head_groups;
   if (flat) {
@@ -398,7 +549,8 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
       const long long U = (long long)hsubs * TP;
       const long long u0 = (long long)r * C;
       st.x = int(min((long long)C, U - u0));
-      st.w = int(u0 / TP);
+      // (64-bit divisions cost a few hundred cycles each; lists below 2^31 units use 32-bit ones)
+      st.w = U <= INT32_MAX ? int(unsigned(u0) / unsigned(TP)) : int(u0 / TP);
       const int rem = int(u0 - (long long)st.w * TP);
       int lo = 0, hi = p.num_seqs;  // cum[lo] <= rem < cum[hi]
       while (hi - lo > 1) {
@@ -414,6 +566,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
     const int4 st = start_range(my_number);
     if (lane == 0) s_iter[warp] = st;
   }
+  if (lane == 0) s_ntodo[warp] = 0;
   __syncwarp();
   const uint64_t policy = policy_evict_first();
   const char* kc_base = static_cast<const char*>(p.kc);
@@ -479,9 +632,16 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
     it.hg = st.w % p.head_groups;
     // the ranges that meet this (head, sequence) are consecutive; each delivers one partial
     const long long base = (long long)st.w * TP + c0;
-    const int w_lo = int(base / C);
-    it.nparts = int((base + n - 1) / C) - w_lo + 1;
-    it.part = int((base + st.y) / C) - w_lo;
+    if (base + n <= INT32_MAX) {  // (32-bit divisions: see start_range)
+      const unsigned b32 = unsigned(base), c32 = unsigned(C);
+      const int w_lo = int(b32 / c32);
+      it.nparts = int((b32 + unsigned(n) - 1u) / c32) - w_lo + 1;
+      it.part = int((b32 + unsigned(st.y)) / c32) - w_lo;
+    } else {
+      const int w_lo = int(base / C);
+      it.nparts = int((base + n - 1) / C) - w_lo + 1;
+      it.part = int((base + st.y) / C) - w_lo;
+    }
     it.first_page = st.y;
     it.tok_begin = st.y * B;
     it.tok_end = max(it.tok_begin, min(len, (st.y + take) * B));
@@ -965,52 +1125,52 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
     // ---- split sequences: the warp that delivers the LAST partial of a (sequence, kv head,
     // head group) merges all of them into `out` (replaces the reference's separate
     // paged_attention_v2_reduce_kernel launch, attention_kernels.cuh:559-664).  Nobody waits:
-    // earlier arrivers just leave.
+    // earlier arrivers just leave.  The arrival is counted here; the merge itself is noted down
+    // and done after the page loop (below), where it costs the loop no registers.  A range has
+    // at most two pieces of sequences that continue in other ranges (its first and its last),
+    // so two notes per warp are enough.
     if (!direct && p.arrive != nullptr) {
       __threadfence();  // partials visible before the arrival is counted
       __syncwarp();
       const size_t unit = (size_t(cur.seq) * p.num_kv_heads + cur.kvh) * p.head_groups + cur.hg;
-      const int64_t rowbase = (int64_t(cur.seq) * p.num_heads + hq0) * p.max_partitions;
-      QT* tmp_q = static_cast<QT*>(p.tmp_out);
-      int np_top = cur.nparts, stride_top = 1;
-      bool go_top = true;
-      if (p.arrive2 != nullptr && cur.nparts > kMergeDirectMax) {
-        // two levels: this piece's group first
+      int level = -1;  // 1: this warp completed its group, 0: it completed the sequence
+      if (p.arrive2 != nullptr && cur.nparts > kMergeDirectMax &&
+          min(kMergeFan, cur.nparts - (cur.part / kMergeFan) * kMergeFan) > 1) {
         const int gidx = cur.part / kMergeFan;
         const int gsize = min(kMergeFan, cur.nparts - gidx * kMergeFan);
-        np_top = (cur.nparts + kMergeFan - 1) / kMergeFan;
-        stride_top = kMergeFan;
-        if (gsize > 1) {
-          unsigned* cnt2 = p.arrive2 + unit * p.groups_max + gidx;
-          unsigned old2 = 0;
-          if (lane == 0) old2 = atomicAdd(cnt2, 1u);
-          old2 = __shfl_sync(0xffffffffu, old2, 0);
-          go_top = old2 == unsigned(gsize - 1);
-          if (go_top) {
-            if (lane == 0) *cnt2 = 0;  // re-arm for the next launch
-            __threadfence();           // order the loads below after the observed arrivals
-            const int64_t g0 = rowbase + gidx * kMergeFan;
-            merge_partials<QT, D>(p.exp_sums, p.max_logits, tmp_q, tmp_q + g0 * D,
-                                  int64_t(p.max_partitions) * D, g0, gsize, p.max_partitions, 1,
-                                  nheads, lane, nullptr, 0, true);
-            __threadfence();
-            __syncwarp();
-          }
+        unsigned* cnt2 = p.arrive2 + unit * p.groups_max + gidx;
+        unsigned old2 = 0;
+        if (lane == 0) old2 = atomicAdd(cnt2, 1u);
+        old2 = __shfl_sync(0xffffffffu, old2, 0);
+        if (old2 == unsigned(gsize - 1)) {
+          if (lane == 0) *cnt2 = 0;  // re-arm for the next launch
+          level = 1;
         }
-      }
-      if (go_top) {
+      } else {
+        const int np_top = (p.arrive2 != nullptr && cur.nparts > kMergeDirectMax)
+                               ? (cur.nparts + kMergeFan - 1) / kMergeFan
+                               : cur.nparts;
         unsigned* cnt = p.arrive + unit;
         unsigned old = 0;
         if (lane == 0) old = atomicAdd(cnt, 1u);
         old = __shfl_sync(0xffffffffu, old, 0);
         if (old == unsigned(np_top - 1)) {
           if (lane == 0) *cnt = 0;  // re-arm for the next launch
-          __threadfence();          // order the loads below after the observed arrivals
-          merge_partials<QT, D>(p.exp_sums, p.max_logits, tmp_q,
-                                static_cast<QT*>(p.out) + (int64_t(cur.seq) * p.num_heads + hq0) * D, D,
-                                rowbase, np_top, p.max_partitions, stride_top, nheads, lane,
-                                p.lse ? p.lse + int64_t(hq0) * p.num_seqs + cur.seq : nullptr,
-                                p.num_seqs, false);
+          level = 0;
+        }
+      }
+      if (level >= 0) {
+        const int n = s_ntodo[warp];
+        if (n < 2) {
+          if (lane == 0) {
+            s_todo[warp][n] = make_int4(cur.seq, cur.kvh * p.head_groups + cur.hg, cur.nparts,
+                                        cur.part | (level << 30));
+            s_ntodo[warp] = n + 1;
+          }
+          __syncwarp();
+        } else {
+          // cannot happen (see above); never drop a merge silently
+          if (lane == 0) atomicExch(p.status, kStatusMergeNotes);
         }
       }
     }
@@ -1026,6 +1186,51 @@ __global__ void __launch_bounds__(MAXW * 32, 1) pa_decode_kernel(const DecodePar
     // the producer either already works on the new `cur` (keep its state) or starts it now
     if (prod_sel == 1) prod_sel = 0; else producer_take(cur);
     while (inflight < NSLOT && produce_one()) {}
+  }
+
+  // ---- the merges this warp owes (noted above)
+  if (!failed) {
+    const int ntodo = s_ntodo[warp];
+    for (int k = 0; k < ntodo; ++k) {
+      const int4 td = s_todo[warp][k];
+      const int seq = td.x, kvh = td.y / p.head_groups, hg = td.y % p.head_groups, nparts = td.z;
+      const int part = td.w & 0x3fffffff;
+      const bool group_first = (td.w >> 30) != 0;
+      const int hq0 = kvh * p.group + hg * TR::kHeadsPerItem;
+      const int nheads = min(TR::kHeadsPerItem, p.group - hg * TR::kHeadsPerItem);
+      const size_t unit = (size_t(seq) * p.num_kv_heads + kvh) * p.head_groups + hg;
+      const int64_t rowbase = (int64_t(seq) * p.num_heads + hq0) * p.max_partitions;
+      QT* tmp_q = static_cast<QT*>(p.tmp_out);
+      const bool two_level = p.arrive2 != nullptr && nparts > kMergeDirectMax;
+      const int np_top = two_level ? (nparts + kMergeFan - 1) / kMergeFan : nparts;
+      const int stride_top = two_level ? kMergeFan : 1;
+      bool go_top = true;
+      if (group_first) {
+        // two levels: this piece's group first, then the group arrives for the sequence
+        const int gidx = part / kMergeFan;
+        const int gsize = min(kMergeFan, nparts - gidx * kMergeFan);
+        __threadfence();  // order the loads below after the observed arrivals
+        const int64_t g0 = rowbase + gidx * kMergeFan;
+        merge_partials<QT, D>(p.exp_sums, p.max_logits, tmp_q, tmp_q + g0 * D,
+                              int64_t(p.max_partitions) * D, g0, gsize, p.max_partitions, 1, nheads,
+                              lane, nullptr, 0, true);
+        __threadfence();
+        __syncwarp();
+        unsigned* cnt = p.arrive + unit;
+        unsigned old = 0;
+        if (lane == 0) old = atomicAdd(cnt, 1u);
+        old = __shfl_sync(0xffffffffu, old, 0);
+        go_top = old == unsigned(np_top - 1);
+        if (go_top && lane == 0) *cnt = 0;  // re-arm for the next launch
+      }
+      if (go_top) {
+        __threadfence();  // order the loads below after the observed arrivals
+        merge_partials<QT, D>(p.exp_sums, p.max_logits, tmp_q,
+                              static_cast<QT*>(p.out) + (int64_t(seq) * p.num_heads + hq0) * D, D, rowbase,
+                              np_top, p.max_partitions, stride_top, nheads, lane,
+                              p.lse ? p.lse + int64_t(hq0) * p.num_seqs + seq : nullptr, p.num_seqs, false);
+      }
+    }
   }
 
   if (failed) {
