@@ -376,6 +376,113 @@ __device__ __noinline__ void merge_partials_fast(float* exp_sums, float* max_log
   }
 }
 
+// The same idea for at most 32 output units (one or two heads of 128): several lanes share a
+// unit and split its partials between them, their sums are added by shuffles.
+template <typename QT, int D, int JB>
+__device__ __noinline__ void merge_partials_fast_few(float* exp_sums, float* max_logits, const QT* tmp,
+                                                     QT* outp, int64_t out_head_stride, int64_t row0, int np,
+                                                     int P, int pstride, int nh, int lane, float* lse,
+                                                     int lse_stride, bool group) {
+  constexpr bool kOutBf = std::is_same_v<QT, __nv_bfloat16>;
+  constexpr int UPH = D / 8;  // units per head
+  const int units = nh * UPH;
+  const int64_t jstep = int64_t(pstride) * D;
+  float ml0[4], es0[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const bool ok = k < nh && lane < np;
+    const int64_t at = row0 + int64_t(ok ? k : 0) * P + int64_t(ok ? lane : 0) * pstride;
+    ml0[k] = ok ? __ldcg(max_logits + at) : -INFINITY;
+    es0[k] = ok ? __ldcg(exp_sums + at) : 0.f;
+  }
+  int u2 = 1;
+  while (u2 < units) u2 <<= 1;
+  const int lpu = 32 / u2;  // lanes per unit
+  const int unit = lane & (u2 - 1);
+  const int sub = lane / u2;
+  const bool uok = unit < units;
+  const int uu = uok ? unit : 0;
+  const int hl = uu / UPH;
+  const int e0 = (uu % UPH) * 8;
+  const QT* src = tmp + (row0 + int64_t(hl) * P) * D + e0;
+  uint4 v[JB];
+  auto request = [&](int jb) {
+#pragma unroll
+    for (int jj = 0; jj < JB; ++jj) {
+      const int j = jb + jj * lpu + sub;
+      if (j < np && uok) v[jj] = __ldcg(reinterpret_cast<const uint4*>(src + int64_t(j) * jstep));
+    }
+  };
+  request(0);
+  float wn[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    float mx = ml0[k];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const float w = (k < nh && lane < np) ? es0[k] * fast_exp2(ml0[k] - mx) : 0.f;
+    float sum = w;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    wn[k] = w * __fdividef(1.f, group ? sum : sum + 1e-6f);
+    if (k < nh && lane == 0) {
+      if (group) {
+        max_logits[row0 + int64_t(k) * P] = mx;
+        exp_sums[row0 + int64_t(k) * P] = sum;
+      } else if (lse != nullptr) {
+        lse[int64_t(k) * lse_stride] = (mx + log2f(sum)) * kLn2;
+      }
+    }
+  }
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  for (int jb = 0; jb < np; jb += JB * lpu) {
+    if (jb > 0) request(jb);
+#pragma unroll
+    for (int jj = 0; jj < JB; ++jj) {
+      if (jb + jj * lpu >= np) break;  // warp-uniform: no lane has a partial at this step
+      const int j = jb + jj * lpu + sub;
+      const int jc = j < np ? j : 0;
+      const float s0 = __shfl_sync(0xffffffffu, wn[0], jc);
+      const float s1 = __shfl_sync(0xffffffffu, wn[1], jc);
+      const float s2 = __shfl_sync(0xffffffffu, wn[2], jc);
+      const float s3 = __shfl_sync(0xffffffffu, wn[3], jc);
+      if (j < np && uok) {
+        const float w = hl == 0 ? s0 : (hl == 1 ? s1 : (hl == 2 ? s2 : s3));
+        const uint32_t vv[4] = {v[jj].x, v[jj].y, v[jj].z, v[jj].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float f0, f1;
+          if constexpr (kOutBf) {
+            f0 = __uint_as_float(vv[i] << 16);
+            f1 = __uint_as_float(vv[i] & 0xffff0000u);
+          } else {
+            const __half2 h = *reinterpret_cast<const __half2*>(&vv[i]);
+            f0 = __low2float(h);
+            f1 = __high2float(h);
+          }
+          acc[2 * i] += w * f0;
+          acc[2 * i + 1] += w * f1;
+        }
+      }
+    }
+  }
+  for (int o = u2; o < 32; o <<= 1) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
+  }
+  __syncwarp();  // (group) partial 0 is a source of other lanes' loads and the destination
+  if (uok && sub == 0) {
+    uint4 o4;
+    o4.x = pack2<kOutBf>(acc[0], acc[1]);
+    o4.y = pack2<kOutBf>(acc[2], acc[3]);
+    o4.z = pack2<kOutBf>(acc[4], acc[5]);
+    o4.w = pack2<kOutBf>(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(outp + hl * out_head_stride + e0) = o4;
+  }
+}
+
 // The merge of one (sequence, kv head, head group).  Both forms are out of line, each with its
 // own register frame, and called after the page loop only (a call from inside it made the
 // compiler spill the loop's state around the call).
@@ -386,15 +493,23 @@ __device__ __forceinline__ void merge_partials(float* exp_sums, float* max_logit
                                             int lse_stride, bool group) {
   constexpr int UPH = D / 8;
   constexpr int HB = UPH <= 16 ? 4 : 2;  // heads per pass: at most 64 output units
-  // Measured on B200: with more than 32 output units (three or more heads of 128) the form that
-  // requests statistics and partials together is faster (an 8-way kv-head shard of a
-  // long-context batch 65 -> 60.5 us); with fewer, where the general form lets several lanes
-  // share a unit, it is slower (MHA decode of 8 sequences 25.6 -> 27.4 us).  Four partials per
-  // round trip: with eight the function needs so many registers that the compiler spills in
-  // the kernel around the call, and the launch with few heads pays for it (29 us).
-  if (np > 32 || nheads * UPH <= 32) {
+  // Up to 32 partials: the forms that request statistics and partials together (measured on
+  // B200 against the general form: MHA decode of 8 sequences 27.5 -> 25.2 us, an 8-way kv-head
+  // shard of a long-context batch 65 -> 60.5 us).  Four partials per request and lane: with eight
+  // the functions need so many registers that the compiler spills in the kernel around the
+  // calls, which costs more than the round trip saves.
+  if (np > 32) {
     merge_partials_general<QT, D>(exp_sums, max_logits, tmp, outp, out_head_stride, row0, np, P, pstride,
                                   nheads, lane, lse, lse_stride, group);
+    return;
+  }
+  if (nheads * UPH <= 32) {
+    for (int h0 = 0; h0 < nheads; h0 += 4) {  // (the forms carry the weights of four heads)
+      float* lse_h = lse ? lse + int64_t(h0) * lse_stride : nullptr;
+      merge_partials_fast_few<QT, D, 4>(exp_sums, max_logits, tmp, outp + h0 * out_head_stride, out_head_stride,
+                                        row0 + int64_t(h0) * P, np, P, pstride, min(4, nheads - h0), lane, lse_h,
+                                        lse_stride, group);
+    }
     return;
   }
   for (int h0 = 0; h0 < nheads; h0 += HB) {
