@@ -558,6 +558,9 @@ def test_skewed_lengths_split_by_equal_block_counts():
         (32, 8, [5, 4000, 3, 2, 9000, 1]),
         (4, 4, list(rng.integers(1, 60, size=300))),
         (16, 1, [12000, 12001, 11999]),
+        # so many (sequence, kv head) pairs that the two-level merge has no counters for them:
+        # the long sequence's 70-odd partials are merged in one go, by the general merge form
+        (8, 8, [40000] + [20] * 999),
     ):
         lens = np.array(lens)
         w = W.make_decode("skew", num_seqs=len(lens), num_heads=hq, num_kv_heads=hkv, head_size=128,
