@@ -692,21 +692,29 @@ static bool launch_staged(const b200pa_cache_args& a, cudaStream_t stream, int* 
     p.num_heads = a.num_heads;
     p.head_size = D;
     p.block_size = a.block_size;
-    p.pitch = D * 2 + 16;
-    p.stage_bytes = kStagedTile * p.pitch + 128;
+    p.hsplit = 1;
     p.nstages = 2;
     int max_warps = kStagedMaxWarps;
     {  // developer knobs, read once
+      static const int kn_hsplit = [] { const char* e = getenv("B200PA_TUNE_KVW_HSPLIT"); return e ? atoi(e) : 0; }();
+      // Small writes (decode steps) are bound by the latency of one work item: half a head per
+      // item while that still leaves every item a warp of its own (measured: 256 scattered
+      // tokens 14.0 -> 11.2 us); large ones pay for the doubled per-item bookkeeping (27 -> 35 us).
+      const int64_t items1 = int64_t((a.num_tokens + kStagedTile - 1) / kStagedTile) * a.num_heads * 2;
+      const bool small = 2 * items1 <= int64_t(cache_sm_count()) * kStagedMaxWarps;
+      if (D % 128 == 0 && (kn_hsplit == 2 || (kn_hsplit == 0 && small))) p.hsplit = 2;
       static const int kn_stages = [] { const char* e = getenv("B200PA_TUNE_KVW_STAGES"); return e ? atoi(e) : 0; }();
       static const int kn_warps = [] { const char* e = getenv("B200PA_TUNE_KVW_WARPS"); return e ? atoi(e) : 0; }();
       if (kn_stages >= 1 && kn_stages <= 8) p.nstages = kn_stages;
       if (kn_warps >= 4 && kn_warps <= kStagedMaxWarps) max_warps = kn_warps;
     }
+    p.pitch = D / p.hsplit * 2 + 16;
+    p.stage_bytes = kStagedTile * p.pitch + 128;
     const size_t budget = 220 * 1024;
     int warps = int(std::min<size_t>(max_warps, (budget - 1024) / (size_t(p.nstages) * p.stage_bytes)));
     warps &= ~3;
     if (warps < 4) return false;
-    const int64_t items = int64_t((a.num_tokens + kStagedTile - 1) / kStagedTile) * a.num_heads * 2;
+    const int64_t items = int64_t((a.num_tokens + kStagedTile - 1) / kStagedTile) * a.num_heads * p.hsplit * 2;
     // few items (decode steps): one per warp, spread over the SMs
     const int sms = cache_sm_count();
     const int per_cta = int(std::min<int64_t>(warps, std::max<int64_t>(4, ((items + sms - 1) / sms + 3) & ~3)));

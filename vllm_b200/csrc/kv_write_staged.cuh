@@ -48,6 +48,7 @@ struct StagedWriteParams {
   int nstages;
   int pitch;        // bytes between two token rows of a stage
   int stage_bytes;  // 16 rows + slot table
+  int hsplit;       // pieces a head's row is cut into (1 or 2): each piece is a work item
 };
 
 constexpr int kStagedTile = 16;  // tokens per work item
@@ -83,13 +84,16 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
   const int H = p.num_heads;
   const int B = p.block_size;
   const int NST = p.nstages;
-  const int row_bytes = D * 2;
+  const int HS = p.hsplit;
+  const int DP = D / HS;  // head dimensions of one work item
+  const int row_bytes = DP * 2;
   const int b_shift = (B & (B - 1)) == 0 ? 31 - __clz(B) : -1;
   const int tiles = (p.num_tokens + kStagedTile - 1) / kStagedTile;
   // Items: the (tile, head) pairs of K, then those of V, dealt out SM-first.  Every warp walks
   // through both halves, so the K and V work (which differ in cost in the x-layout) is spread
   // evenly over warps and SMs.
-  const unsigned pairs = unsigned(tiles) * unsigned(H);
+  const unsigned HH = unsigned(H) * unsigned(HS);  // (head, piece of the head) pairs per tile
+  const unsigned pairs = unsigned(tiles) * HH;
   const unsigned items = pairs * 2u;
   const unsigned grid_warps = gridDim.x * unsigned(nwarps);
   unsigned next_item = unsigned(warp) * gridDim.x + blockIdx.x;
@@ -118,7 +122,7 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
   // statement: the compiler would otherwise move it down to its use.
   auto load_slot = [&](unsigned item) -> int64_t {
     if (item >= items) return -1;
-    const int tile = int((item >= pairs ? item - pairs : item) / unsigned(H));
+    const int tile = int((item >= pairs ? item - pairs : item) / HH);
     const int tok = tile * kStagedTile + (lane & 15);
     if (tok >= p.num_tokens) return -1;
     int64_t v;
@@ -131,8 +135,8 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
   auto produce = [&](unsigned item, int stage) {
     const bool is_v = item >= pairs;
     const unsigned pr = is_v ? item - pairs : item;
-    const int tile = int(pr / unsigned(H));
-    const int h = int(pr - unsigned(tile) * unsigned(H));
+    const int tile = int(pr / HH);
+    const int hp = int(pr - unsigned(tile) * HH);  // head * HS + piece
     const int t = lane & 15;
     const int tok = tile * kStagedTile + t;
     const int64_t slot = slot_a;
@@ -147,7 +151,7 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
     __syncwarp();  // the expectation is set before any copy can complete on the barrier
     if (valid) {
       const char* src = (is_v ? val_b : key_b) +
-                        (int64_t(tok) * (is_v ? p.value_stride : p.key_stride) + int64_t(h) * D) * 2;
+                        (int64_t(tok) * (is_v ? p.value_stride : p.key_stride) + int64_t(hp) * DP) * 2;
       bulk_g2s(smem_u32(st) + t * p.pitch, src, uint32_t(row_bytes), bar, policy);
     }
   };
@@ -182,7 +186,9 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
     const unsigned char* st = my_stages + size_t(cons_stage) * p.stage_bytes;
     const bool is_v = cur_item >= pairs;
     const unsigned cur_pr = is_v ? cur_item - pairs : cur_item;
-    const int h = int(cur_pr % unsigned(H));
+    const int hp = int(cur_pr % HH);
+    const int h = hp / HS;
+    const int piece = hp - h * HS;
     // lane t (and t + 16) knows token t's cache block and offset
     const int64_t slot = reinterpret_cast<const int64_t*>(st + slot_off)[lane & 15];
     const bool valid = slot >= 0;
@@ -193,7 +199,9 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
 
     if (kFlash || !is_v) {
       // ================= K (and V of the flash layout): 16-byte chunks, tokens first
-      const int chunks = D / CH;
+      const int chunks = D / CH;       // of the whole head
+      const int my_chunks = DP / CH;   // of this item
+      const int c_first = piece * my_chunks;
       const int t = lane & 15;
       const ScaledDiv& div = is_v ? v_div : k_div;
       const unsigned char* rows = st + t * p.pitch;
@@ -209,9 +217,9 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
         cstep = int64_t(B) * 16;
       }
       if (valid) {
-        for (int c = lane >> 4; c < chunks; c += 2) {
+        for (int c = lane >> 4; c < my_chunks; c += 2) {
           const uint4 v = staged_chunk<in_t, cache_t, KV>(rows + c * CHB, div);
-          *reinterpret_cast<uint4*>(dst + c * cstep) = v;
+          *reinterpret_cast<uint4*>(dst + (c_first + c) * cstep) = v;
         }
       }
     } else {
@@ -234,12 +242,14 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
       const unsigned char* vrows = st;
       // every lane runs every iteration (the stores below use warp shuffles); lanes whose pair
       // of rows lies beyond the head size only take part in those
-      for (int d_base = 0; d_base < D; d_base += 64) {
-        const int d0 = d_base + 2 * lane;
-        const bool mine = d0 < D;
+      const int d_first = piece * DP;
+      for (int d_base = 0; d_base < DP; d_base += 64) {
+        const int dl = d_base + 2 * lane;  // inside the item
+        const int d0 = d_first + dl;       // inside the head
+        const bool mine = dl < DP;
         uint32_t two[kStagedTile];  // token t: (d0, d0 + 1)
         if (mine) {
-          const unsigned char* col = vrows + d0 * 2;
+          const unsigned char* col = vrows + dl * 2;
           const int pitch = p.pitch;
 #pragma unroll
           for (int t = 0; t < kStagedTile; ++t) two[t] = *reinterpret_cast<const uint32_t*>(col + t * pitch);
