@@ -236,18 +236,23 @@ def test_reshape_and_cache_random_shapes_and_slot_patterns(seed):
     assert same(kf, kfo) and same(vf, vfo), ("flash layout", dtype, kv, block_size, H, head_size, T, pattern)
 
 
-@pytest.mark.parametrize("staged", ["0", "1"])
-def test_both_kv_write_implementations(staged):
+@pytest.mark.parametrize("knobs", [
+    {"B200PA_TUNE_KVW_STAGED": "0"},
+    {"B200PA_TUNE_KVW_STAGED": "1", "B200PA_TUNE_KVW_HSPLIT": "1"},
+    {"B200PA_TUNE_KVW_STAGED": "1", "B200PA_TUNE_KVW_HSPLIT": "2"},
+], ids=["plain", "staged-whole-heads", "staged-half-heads"])
+def test_both_kv_write_implementations(knobs):
     """The library has two implementations of the KV write (plain loads; rows staged through
-    shared memory by bulk async copies) and picks one per call by layout, cache type and size.
-    B200PA_TUNE_KVW_STAGED forces one of them for every call that it can take; it is read once
-    per process, so the parity tests of this file run again in a child process for each setting."""
+    shared memory by bulk async copies, with a whole head or half a head of 128 per work item)
+    and picks per call by layout, cache type and size.  B200PA_TUNE_KVW_STAGED / _HSPLIT force
+    one for every call that it can take; they are read once per process, so the parity tests of
+    this file run again in a child process for each setting."""
     import os
     import subprocess
     import sys
     from pathlib import Path
     root = Path(__file__).resolve().parents[1]
-    env = dict(os.environ, B200PA_TUNE_KVW_STAGED=staged)
+    env = dict(os.environ, **knobs)
     r = subprocess.run(
         [sys.executable, "-m", "pytest", str(Path(__file__)), "-q", "-x", "-m", "gpu", "-p", "no:cacheprovider",
          "-k", "not both_kv_write", str(root / "tests" / "test_full_size_gpu.py") + "::test_full_size_kv_write_round_trip"],
