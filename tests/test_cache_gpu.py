@@ -7,6 +7,7 @@ import torch
 
 from oracle import paged_oracle as O
 from vllm_b200 import _custom_ops as ops
+from vllm_b200 import capi
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -234,6 +235,45 @@ def test_reshape_and_cache_random_shapes_and_slot_patterns(seed):
     kfo, vfo = torch.zeros(kf.shape, dtype=cdt), torch.zeros(vf.shape, dtype=cdt)
     O.reshape_and_cache_flash(key.cpu(), val.cpu(), kfo, vfo, slots_t.cpu(), kv, float(ks), float(vs))
     assert same(kf, kfo) and same(vf, vfo), ("flash layout", dtype, kv, block_size, H, head_size, T, pattern)
+
+
+@pytest.mark.parametrize("kv", ["auto", "fp8"])
+@pytest.mark.parametrize("block_size", [16, 32])
+def test_prefill_chunks_that_start_inside_a_block(kv, block_size):
+    """A large write whose sequences start at arbitrary offsets inside their first block (the
+    continuation of earlier context): 16-token tiles that straddle cache blocks, runs of every
+    length that follow each other, some tokens padding."""
+    rng = np.random.default_rng(77 + block_size)
+    H, D = 8, 128
+    lens = [300, 17, 16, 15, 1, 700, 33, 64, 5, 2, 1000, 31, 48, 260, 129, 500, 1029]
+    starts, slots, pos = [], [], 0
+    for n in lens:
+        pos = (pos + block_size - 1) // block_size * block_size + int(rng.integers(0, block_size))
+        slots.append(np.arange(pos, pos + n, dtype=np.int64))
+        pos += n + int(rng.integers(0, 3)) * block_size
+        if rng.integers(0, 3) == 0:
+            slots.append(np.full(int(rng.integers(1, 20)), -1, dtype=np.int64))
+    slots = np.concatenate(slots)
+    T = len(slots)
+    NB = int(slots.max()) // block_size + 2
+    fp8 = kv != "auto"
+    g = torch.Generator(device=DEV).manual_seed(9)
+    key = torch.randn(T, H, D, device=DEV, generator=g).mul(2).to(torch.bfloat16)
+    val = torch.randn(T, H, D, device=DEV, generator=g).mul(2).to(torch.bfloat16)
+    slots_t = torch.from_numpy(slots).to(DEV)
+    ks, vs = torch.tensor(0.0173, device=DEV), torch.tensor(0.0291, device=DEV)
+    cdt = torch.uint8 if fp8 else torch.bfloat16
+    x = 16 // (1 if fp8 else 2)
+    kc = torch.zeros(NB, H, D // x, block_size, x, dtype=cdt, device=DEV)
+    vc = torch.zeros(NB, H, D, block_size, dtype=cdt, device=DEV)
+    for _ in range(2):  # (twice: the second call overwrites with the same bytes)
+        ops.reshape_and_cache(key, val, kc, vc, slots_t, kv, ks, vs)
+    kco, vco = torch.zeros_like(kc, device="cpu"), torch.zeros_like(vc, device="cpu")
+    O.reshape_and_cache(key.cpu(), val.cpu(), kco, vco, slots_t.cpu(), kv, float(ks), float(vs))
+    same = lambda a, b: torch.equal(a.cpu().contiguous().view(torch.uint8), b.cpu().contiguous().view(torch.uint8))
+    assert same(kc, kco), "key cache"
+    assert same(vc, vco), "value cache"
+    assert capi.device_status() == 0
 
 
 @pytest.mark.parametrize("knobs", [
