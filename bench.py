@@ -361,8 +361,8 @@ def write_case(w, layout: str, kv: str, steps: int, warmup: int, peaks, tokens=N
     """Times the KV write of config 3's shape: `layout` x|flash, cache type `kv` fp8|auto,
     `tokens` = None for the prefill-shaped write (128 new tokens per sequence, consecutive
     slots) or a count for a decode-shaped one (that many scattered slots, one per sequence);
-    `shift` moves every slot down by that many positions, so that the 16-token tiles of the
-    prefill-shaped write straddle cache blocks (sequences that do not start on a block edge)."""
+    `shift` writes the new tokens that many positions earlier in their sequences, so that the
+    chunk of each sequence starts inside a cache block (the continuation of earlier context)."""
     from vllm_b200 import _custom_ops as ops
 
     dev = w.query.device
@@ -375,7 +375,13 @@ def write_case(w, layout: str, kv: str, steps: int, warmup: int, peaks, tokens=N
         pick = pick.repeat(reps)[:tokens]
         nk, nv, sm = nk[pick].contiguous(), nv[pick].contiguous(), sm[pick].contiguous()
     if shift:
-        sm = sm - shift
+        # the same number of new tokens per sequence, `shift` positions earlier: positions
+        # [len - new - shift, len - shift), through the sequence's block table
+        per = nk.shape[0] // w.num_seqs
+        L = int(w.seq_lens[0])
+        pos = torch.arange(L - per - shift, L - shift, device=dev)
+        bt = w.block_tables.long()
+        sm = (bt[:, pos // w.block_size] * w.block_size + (pos % w.block_size).view(1, -1)).reshape(-1).contiguous()
     T = nk.shape[0]
     nb, B, H, D = w.key_cache.shape[0], w.block_size, w.num_kv_heads, w.head_size
     cdt = torch.uint8 if kv == "fp8" else nk.dtype

@@ -278,14 +278,18 @@ def test_prefill_chunks_that_start_inside_a_block(kv, block_size):
 
 @pytest.mark.parametrize("knobs", [
     {"B200PA_TUNE_KVW_STAGED": "0"},
-    {"B200PA_TUNE_KVW_STAGED": "1", "B200PA_TUNE_KVW_HSPLIT": "1"},
-    {"B200PA_TUNE_KVW_STAGED": "1", "B200PA_TUNE_KVW_HSPLIT": "2"},
-], ids=["plain", "staged-whole-heads", "staged-half-heads"])
+    {"B200PA_TUNE_KVW_STAGED": "1", "B200PA_TUNE_KVW_HSPLIT": "1", "B200PA_TUNE_KVW_SHIFT": "0"},
+    {"B200PA_TUNE_KVW_STAGED": "1", "B200PA_TUNE_KVW_HSPLIT": "2", "B200PA_TUNE_KVW_SHIFT": "0"},
+    {"B200PA_TUNE_KVW_STAGED": "1", "B200PA_TUNE_KVW_HSPLIT": "1", "B200PA_TUNE_KVW_SHIFT": "1"},
+    {"B200PA_TUNE_KVW_STAGED": "1", "B200PA_TUNE_KVW_HSPLIT": "2", "B200PA_TUNE_KVW_SHIFT": "1"},
+], ids=["plain", "staged-whole-heads", "staged-half-heads", "staged-whole-heads-moved-tiles",
+        "staged-half-heads-moved-tiles"])
 def test_both_kv_write_implementations(knobs):
     """The library has two implementations of the KV write (plain loads; rows staged through
     shared memory by bulk async copies, with a whole head or half a head of 128 per work item)
-    and picks per call by layout, cache type and size.  B200PA_TUNE_KVW_STAGED / _HSPLIT force
-    one for every call that it can take; they are read once per process, so the parity tests of
+    and picks per call by layout, cache type and size; large x-layout writes use a variant that
+    moves 16-token tiles onto 16-slot boundaries of the cache.  B200PA_TUNE_KVW_STAGED / _HSPLIT
+    / _SHIFT force one setting for every call that it can take; they are read once per process, so the parity tests of
     this file run again in a child process for each setting."""
     import os
     import subprocess

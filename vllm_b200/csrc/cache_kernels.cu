@@ -656,8 +656,8 @@ static int cache_sm_count() {
 // The staged kernel takes 16-bit key/value tensors whose rows, and the cache's 16-byte chunks,
 // are 16-byte aligned.  Returns false when the call does not qualify (the caller then uses the
 // plain kernels); otherwise launches and stores the return code in *rc.
-template <typename in_t, typename cache_t, int KV, bool kFlash>
-static bool launch_staged(const b200pa_cache_args& a, cudaStream_t stream, int* rc) {
+template <typename in_t, typename cache_t, int KV, bool kFlash, bool kShift>
+static bool launch_staged_as(const b200pa_cache_args& a, cudaStream_t stream, int* rc, int hsplit) {
   if constexpr (sizeof(in_t) != 2 || sizeof(cache_t) > 2) {
     return false;
   } else {
@@ -692,24 +692,17 @@ static bool launch_staged(const b200pa_cache_args& a, cudaStream_t stream, int* 
     p.num_heads = a.num_heads;
     p.head_size = D;
     p.block_size = a.block_size;
-    p.hsplit = 1;
+    p.hsplit = hsplit;
     p.nstages = 2;
     int max_warps = kStagedMaxWarps;
     {  // developer knobs, read once
-      static const int kn_hsplit = [] { const char* e = getenv("B200PA_TUNE_KVW_HSPLIT"); return e ? atoi(e) : 0; }();
-      // Small writes (decode steps) are bound by the latency of one work item: half a head per
-      // item while that still leaves every item a warp of its own (measured: 256 scattered
-      // tokens 14.0 -> 11.2 us); large ones pay for the doubled per-item bookkeeping (27 -> 35 us).
-      const int64_t items1 = int64_t((a.num_tokens + kStagedTile - 1) / kStagedTile) * a.num_heads * 2;
-      const bool small = 2 * items1 <= int64_t(cache_sm_count()) * kStagedMaxWarps;
-      if (D % 128 == 0 && (kn_hsplit == 2 || (kn_hsplit == 0 && small))) p.hsplit = 2;
       static const int kn_stages = [] { const char* e = getenv("B200PA_TUNE_KVW_STAGES"); return e ? atoi(e) : 0; }();
       static const int kn_warps = [] { const char* e = getenv("B200PA_TUNE_KVW_WARPS"); return e ? atoi(e) : 0; }();
       if (kn_stages >= 1 && kn_stages <= 8) p.nstages = kn_stages;
       if (kn_warps >= 4 && kn_warps <= kStagedMaxWarps) max_warps = kn_warps;
     }
     p.pitch = D / p.hsplit * 2 + 16;
-    p.stage_bytes = kStagedTile * p.pitch + 128;
+    p.stage_bytes = kStagedTile * p.pitch + 128 + (kShift ? 16 : 0);
     const size_t budget = 220 * 1024;
     int warps = int(std::min<size_t>(max_warps, (budget - 1024) / (size_t(p.nstages) * p.stage_bytes)));
     warps &= ~3;
@@ -721,7 +714,7 @@ static bool launch_staged(const b200pa_cache_args& a, cudaStream_t stream, int* 
     const int grid = int(std::min<int64_t>(sms, (items + per_cta - 1) / per_cta));
     const size_t smem = ((size_t(per_cta) * p.nstages * 8 + 127) & ~size_t(127)) +
                         size_t(per_cta) * p.nstages * p.stage_bytes;
-    auto kern = kv_write_staged_kernel<in_t, cache_t, KV, kFlash>;
+    auto kern = kv_write_staged_kernel<in_t, cache_t, KV, kFlash, kShift>;
     static bool done[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -746,13 +739,37 @@ static bool launch_staged(const b200pa_cache_args& a, cudaStream_t stream, int* 
   }
 }
 
+// Picks the variant of the staged kernel for a call.
+template <typename in_t, typename cache_t, int KV, bool kFlash>
+static bool launch_staged(const b200pa_cache_args& a, cudaStream_t stream, int* rc) {
+  static const int kn_hsplit = [] { const char* e = getenv("B200PA_TUNE_KVW_HSPLIT"); return e ? atoi(e) : 0; }();
+  static const int kn_shift = [] { const char* e = getenv("B200PA_TUNE_KVW_SHIFT"); return e ? atoi(e) : -1; }();
+  // Small writes (decode steps) are bound by the latency of one work item: half a head per
+  // item while that still leaves every item a warp of its own (measured: 256 scattered
+  // tokens 14.0 -> 11.2 us); large ones pay for the doubled per-item bookkeeping (27 -> 35 us).
+  const int64_t items1 = int64_t((a.num_tokens + kStagedTile - 1) / kStagedTile) * a.num_heads * 2;
+  const bool small = 2 * items1 <= int64_t(cache_sm_count()) * kStagedMaxWarps;
+  const int hsplit = (a.head_size % 128 == 0 && (kn_hsplit == 2 || (kn_hsplit == 0 && small))) ? 2 : 1;
+  // Large x-layout writes use the variant that moves tiles onto 16-slot boundaries of the cache
+  // (prefill chunks that start inside a block: 16 384 tokens x 8 heads, fp8 51 -> 38 us, 16-bit
+  // cache 67 -> 36 us; chunks that start on a boundary are not affected).  Its extra code costs
+  // writes of scattered tokens 3-5 us below 4096 tokens (fp8; nothing from 8192 on), and those
+  // are decode steps, which have no runs to move.
+  bool shift = !kFlash && a.num_tokens >= 4096 && a.block_size % kStagedTile == 0;
+  if (kn_shift >= 0) shift = !kFlash && kn_shift != 0 && a.block_size % kStagedTile == 0;
+  if constexpr (!kFlash) {
+    if (shift) return launch_staged_as<in_t, cache_t, KV, false, true>(a, stream, rc, hsplit);
+  }
+  return launch_staged_as<in_t, cache_t, KV, kFlash, false>(a, stream, rc, hsplit);
+}
+
 template <typename in_t, typename cache_t, int KV>
 static int launch_reshape(const b200pa_cache_args& a, cudaStream_t stream, bool flash) {
   if (a.num_tokens == 0) return B200PA_OK;
   // Two implementations; which one is faster was measured per case on B200 (16 384 tokens x 8
-  // heads x 128, us, staged / plain): x-layout fp8 32 / 31, flash fp8 27 / 29, x-layout 16-bit
-  // cache 30 / 40, 256 scattered tokens (a decode step) 14 / 17, x-layout fp8 with sequences
-  // that do not start on a tile boundary 58 / 92 - and flash with a 16-bit cache 30 / 25, the
+  // heads x 128, us, staged / plain): x-layout fp8 29 / 31, flash fp8 27 / 29, x-layout 16-bit
+  // cache 27 / 40, 256 scattered tokens (a decode step) 11 / 17, x-layout fp8 with sequences
+  // that start inside a block 38 / 92 - and flash with a 16-bit cache 30 / 25, the
   // one case that stays with the plain kernel.  B200PA_TUNE_KVW_STAGED=0/1 forces one of them
   // (for the tests that compare the two).
   static const int kn_staged = [] { const char* e = getenv("B200PA_TUNE_KVW_STAGED"); return e ? atoi(e) : -1; }();

@@ -47,7 +47,7 @@ struct StagedWriteParams {
   int block_size;
   int nstages;
   int pitch;        // bytes between two token rows of a stage
-  int stage_bytes;  // 16 rows + slot table
+  int stage_bytes;  // 16 rows + slot table (+ shifts)
   int hsplit;       // pieces a head's row is cut into (1 or 2): each piece is a work item
 };
 
@@ -70,8 +70,9 @@ __device__ __forceinline__ uint4 staged_chunk(const unsigned char* src, const Sc
   }
 }
 
-template <typename in_t, typename cache_t, int KV, bool kFlash>
+template <typename in_t, typename cache_t, int KV, bool kFlash, bool kShift>
 __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kernel(const StagedWriteParams p) {
+  static_assert(!(kFlash && kShift), "tiles are moved in the x-layout only");
   static_assert(sizeof(in_t) == 2, "16-bit key/value tensors");
   extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int E = sizeof(cache_t);       // 1 (fp8) or 2
@@ -120,17 +121,65 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
   // (`slot_a` belongs to the item that the next produce() call will request, `slot_b` to the one
   // after), so that the producer never waits for that load.  The load is a volatile asm
   // statement: the compiler would otherwise move it down to its use.
+  // kShift: lanes 16 and 17 fetch the first and the last slot of the tile in front as well.
   auto load_slot = [&](unsigned item) -> int64_t {
     if (item >= items) return -1;
     const int tile = int((item >= pairs ? item - pairs : item) / HH);
-    const int tok = tile * kStagedTile + (lane & 15);
-    if (tok >= p.num_tokens) return -1;
+    int tok = tile * kStagedTile + (lane & 15);
+    if constexpr (kShift) {
+      if (lane >= 16) tok = lane < 18 ? (tile - 1) * kStagedTile + (lane & 1) * (kStagedTile - 1) : -1;
+    }
+    if (tok < 0 || tok >= p.num_tokens) return -1;
     int64_t v;
     asm volatile("ld.global.nc.s64 %0, [%1];" : "=l"(v) : "l"(p.slot_mapping + tok));
     return v;
   };
-  int64_t slot_a = load_slot(next_item);
+  // ---- kShift: which 16 tokens an item covers.  A row of V in the x-layout holds the tokens
+  // of one block, so a tile writes whole 16-byte rows only if its tokens fill 16 aligned slots;
+  // the tiles of a prefill chunk that starts inside a block never do.  A tile whose first,
+  // ninth and last token sit at consecutive offsets modulo 16 (consecutive positions of one
+  // sequence, whatever blocks they are in) therefore covers the 16 tokens from the next 16-slot
+  // boundary on: tokens [16 i + shift, 16 i + shift + 16), 0 <= shift < 16.  The tokens
+  // [16 i, 16 i + shift) that it gives up lie in the window of tile i - 1 if that one is shifted
+  // by at least as much - every tile can tell, the shift is a function of a tile's own slots;
+  // otherwise tile i writes them itself from global memory (`head` in the consumer; once per
+  // run).  Windows may overlap: a slot is then written twice with the same bytes.  The rule is
+  // only a guess about the slots; whatever they are, every token is written, with its own slot.
+  auto shift_of = [&](int64_t first, int64_t mid, int64_t last) -> int {
+    if (first < 0 || mid < 0 || last < 0) return 0;
+    if (((mid - first) & 15) != 8 || ((last - first) & 15) != 15) return 0;
+    return int((kStagedTile - (first & 15)) & 15);
+  };
+  // Turns the slots of a tile (as load_slot delivers them) into those of its window; `sh` =
+  // shift | shift of the tile in front << 8.
+  auto to_window = [&](unsigned item, int64_t cand, int& sh) -> int64_t {
+    sh = 0;
+    if constexpr (!kShift) {
+      return cand;
+    } else {
+      if (item >= items) return cand;
+      const int64_t f = __shfl_sync(0xffffffffu, cand, 0), m = __shfl_sync(0xffffffffu, cand, 8);
+      const int64_t l = __shfl_sync(0xffffffffu, cand, 15);
+      const int64_t pf = __shfl_sync(0xffffffffu, cand, 16), pl = __shfl_sync(0xffffffffu, cand, 17);
+      const int d = shift_of(f, m, l);
+      if (d == 0) return cand;  // (the shift of the tile in front does not matter then)
+      // the tile in front: its ninth slot is not at hand; first and last decide
+      const int dp = (pf >= 0 && pl >= 0 && ((pl - pf) & 15) == 15) ? int((kStagedTile - (pf & 15)) & 15) : 0;
+      sh = d | (dp << 8);
+      const int tile = int((item >= pairs ? item - pairs : item) / HH);
+      const int tok = tile * kStagedTile + d + (lane & 15);
+      if (tok >= p.num_tokens) return -1;
+      int64_t v;
+      asm volatile("ld.global.nc.s64 %0, [%1];" : "=l"(v) : "l"(p.slot_mapping + tok));
+      return v;
+    }
+  };
+  int sh_a = 0;
+  int64_t slot_a = to_window(next_item, load_slot(next_item), sh_a);
   int64_t slot_b = load_slot(next_item + grid_warps);
+
+  // a stage: 16 rows, the 16 slots of the tile (window), then the shifts
+  const int sh_off = slot_off + kStagedTile * 8;
 
   auto produce = [&](unsigned item, int stage) {
     const bool is_v = item >= pairs;
@@ -138,12 +187,18 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
     const int tile = int(pr / HH);
     const int hp = int(pr - unsigned(tile) * HH);  // head * HS + piece
     const int t = lane & 15;
-    const int tok = tile * kStagedTile + t;
+    const int sh = sh_a;
+    const int tok = tile * kStagedTile + (sh & 0xff) + t;
     const int64_t slot = slot_a;
-    slot_a = slot_b;
+    // b becomes a (its slots have had an item's time to arrive; a moved window's slots are
+    // requested now and have another)
+    slot_a = to_window(item + grid_warps, slot_b, sh_a);
     slot_b = load_slot(item + 2 * grid_warps);
     unsigned char* st = my_stages + size_t(stage) * p.stage_bytes;
     if (lane < kStagedTile) reinterpret_cast<int64_t*>(st + slot_off)[t] = slot;
+    if constexpr (kShift) {
+      if (lane == 0) *reinterpret_cast<int*>(st + sh_off) = sh;
+    }
     const bool valid = slot >= 0 && lane < kStagedTile;
     const unsigned vmask = __ballot_sync(0xffffffffu, valid);
     const uint32_t bar = my_bar0 + stage * 8;
@@ -196,6 +251,63 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
     const int64_t blk = !valid ? 0 : (b_shift >= 0 ? slot >> b_shift : slot / B);
     const int off = valid ? int(slot - blk * B) : 0;
     const unsigned vmask = __ballot_sync(0xffffffffu, valid) & 0xffffu;
+
+    if constexpr (kShift) {
+      // ---- tokens in front of a moved window that no other window covers (see above): at most
+      // 15, straight from global memory, all loads independent of each other
+      const int sh = *reinterpret_cast<const int*>(st + sh_off);
+      const int tile = int(cur_pr / HH);
+      const int hb = tile * kStagedTile + (tile > 0 ? ((sh >> 8) & 0xff) : 0);
+      const int nh = min(tile * kStagedTile + (sh & 0xff), p.num_tokens) - hb;
+      if (nh > 0) {
+        const int64_t hslot = lane < nh ? p.slot_mapping[hb + lane] : int64_t(-1);
+        const int64_t in_stride = is_v ? p.value_stride : p.key_stride;
+        const unsigned char* rows0 = reinterpret_cast<const unsigned char*>(is_v ? val_b : key_b) +
+                                     (int64_t(hb) * in_stride + int64_t(hp) * DP) * 2;
+        if (!is_v) {
+          const int chunks = D / CH, my_chunks = DP / CH;
+          const int total = nh * my_chunks;
+          for (int base = 0; base < total; base += 32) {  // (uniform trip count: shuffles inside)
+            const int idx = base + lane;
+            const bool act = idx < total;
+            const int k = act ? idx / my_chunks : 0;
+            const int c = idx - k * my_chunks;
+            const int64_t hs = __shfl_sync(0xffffffffu, hslot, k);
+            if (act && hs >= 0) {
+              const int64_t hblk = b_shift >= 0 ? hs >> b_shift : hs / B;
+              const int hoff = int(hs - hblk * B);
+              unsigned char* dst = static_cast<unsigned char*>(p.key_cache) +
+                                   (((hblk * H + h) * int64_t(chunks) + piece * my_chunks + c) * B + hoff) * 16;
+              *reinterpret_cast<uint4*>(dst) =
+                  staged_chunk<in_t, cache_t, KV>(rows0 + int64_t(k) * in_stride * 2 + c * CHB, k_div);
+            }
+          }
+        } else {
+          const int quads = DP / 4;  // a lane converts four adjacent d of one token at a time
+          const int total = nh * quads;
+          for (int base = 0; base < total; base += 32) {
+            const int idx = base + lane;
+            const bool act = idx < total;
+            const int k = act ? idx / quads : 0;
+            const int q4 = idx - k * quads;
+            const int64_t hs = __shfl_sync(0xffffffffu, hslot, k);
+            if (act && hs >= 0) {
+              const int64_t hblk = b_shift >= 0 ? hs >> b_shift : hs / B;
+              const int hoff = int(hs - hblk * B);
+              const uint2 raw = __ldg(reinterpret_cast<const uint2*>(rows0 + int64_t(k) * in_stride * 2) + q4);
+              in_t four[4];
+              *reinterpret_cast<uint2*>(four) = raw;
+              cache_t o[4];
+              convert_n<in_t, cache_t, KV, 4>(four, o, v_div);
+              cache_t* dst = static_cast<cache_t*>(p.value_cache) +
+                             ((hblk * H + h) * int64_t(D) + piece * DP + 4 * q4) * B + hoff;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) dst[int64_t(i) * B] = o[i];
+            }
+          }
+        }
+      }
+    }
 
     if (kFlash || !is_v) {
       // ================= K (and V of the flash layout): 16-byte chunks, tokens first
