@@ -19,6 +19,11 @@
 //     adjacent d of all 16 tokens from shared memory, converts the two rows and writes each
 //     with one 16-byte store when the tile fills 16 aligned consecutive slots, else four bytes
 //     at a time where consecutive tokens allow it, else element by element (decode steps);
+//   * small writes cut a head of 128 into two work items (hsplit), which halves the latency of
+//     the one item a warp then has;
+//   * the kShift instantiation (large x-layout writes) moves a tile whose tokens are consecutive
+//     positions of a sequence onto the next 16-slot boundary of the cache, so that prefill
+//     chunks which start inside a block still write whole rows of V (details at `shift_of`);
 //   * every mbarrier wait is bounded; a wait that runs out records a status code and the warp
 //     leaves.
 #pragma once
