@@ -594,7 +594,7 @@ def main() -> int:
         units_rank = T
         bytes_rank = w.reshape_bytes()
         metric = "reshape_and_cache tokens/s"
-        kernel_name = "reshape_and_cache_flash_kernel" if version == "cfg3wf" else "reshape_and_cache_kernel"
+        kernel_name = "kv_write_staged_kernel (reshape_and_cache%s)" % ("_flash" if version == "cfg3wf" else "")
         cfg["workload"] = (f"{w.name} KV write ({'flash' if version == 'cfg3wf' else 'x'} layout): "
                            f"{T} new tokens x {w.num_kv_heads} heads x {w.head_size}, bf16 -> fp8-e4m3, "
                            f"block_size={w.block_size}")
