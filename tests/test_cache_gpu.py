@@ -276,6 +276,57 @@ def test_prefill_chunks_that_start_inside_a_block(kv, block_size):
     assert capi.device_status() == 0
 
 
+@pytest.mark.parametrize("seed", range(16))
+def test_large_mixed_batches_of_chunks_and_single_tokens(seed):
+    """Large writes (the size range in which tiles are moved onto 16-slot boundaries) made of
+    prefill chunks of random length at random offsets, single decode tokens and padding, in
+    random order, with random head counts and sizes: every token lands in its own slot."""
+    rng = np.random.default_rng(9000 + seed)
+    block_size = int(rng.choice([16, 32]))
+    H = int(rng.choice([1, 3, 8]))
+    D = int(rng.choice([64, 128, 256]))
+    kv = ["auto", "fp8", "fp8_e5m2"][int(rng.integers(3))]
+    dtype = [torch.bfloat16, torch.float16][int(rng.integers(2))]
+    target = int(rng.choice([4096, 4500, 7000, 10000]))
+    pieces, free = [], 0  # slots are handed out in increasing order, with gaps: no duplicates
+    total = 0
+    while total < target:
+        kind = int(rng.integers(4))
+        if kind == 0:      # a decode token somewhere
+            free += int(rng.integers(1, 5 * block_size))
+            pieces.append(np.array([free], dtype=np.int64))
+            free += 1
+        elif kind == 1:    # padding
+            pieces.append(np.full(int(rng.integers(1, 9)), -1, dtype=np.int64))
+        else:              # a chunk of consecutive positions starting anywhere in a block
+            n = int(rng.integers(1, 400))
+            free += int(rng.integers(0, 3 * block_size))
+            pieces.append(np.arange(free, free + n, dtype=np.int64))
+            free += n
+        total += len(pieces[-1])
+    order = rng.permutation(len(pieces))
+    slots = np.concatenate([pieces[i] for i in order])
+    T = len(slots)
+    NB = free // block_size + 2
+    fp8 = kv != "auto"
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    key = torch.randn(T, H, D, device=DEV, generator=g).mul(2).to(dtype)
+    val = torch.randn(T, H, D, device=DEV, generator=g).mul(2).to(dtype)
+    slots_t = torch.from_numpy(slots).to(DEV)
+    ks, vs = torch.tensor(0.0173, device=DEV), torch.tensor(0.11, device=DEV)
+    cdt = torch.uint8 if fp8 else dtype
+    x = 16 // (1 if fp8 else 2)
+    kc = torch.zeros(NB, H, D // x, block_size, x, dtype=cdt, device=DEV)
+    vc = torch.zeros(NB, H, D, block_size, dtype=cdt, device=DEV)
+    ops.reshape_and_cache(key, val, kc, vc, slots_t, kv, ks, vs)
+    kco, vco = torch.zeros_like(kc, device="cpu"), torch.zeros_like(vc, device="cpu")
+    O.reshape_and_cache(key.cpu(), val.cpu(), kco, vco, slots_t.cpu(), kv, float(ks), float(vs))
+    same = lambda a, b: torch.equal(a.cpu().contiguous().view(torch.uint8), b.cpu().contiguous().view(torch.uint8))
+    assert same(kc, kco), ("key cache", block_size, H, D, kv, dtype, T)
+    assert same(vc, vco), ("value cache", block_size, H, D, kv, dtype, T)
+    assert capi.device_status() == 0
+
+
 @pytest.mark.parametrize("knobs", [
     {"B200PA_TUNE_KVW_STAGED": "0"},
     {"B200PA_TUNE_KVW_STAGED": "1", "B200PA_TUNE_KVW_HSPLIT": "1", "B200PA_TUNE_KVW_SHIFT": "0"},

@@ -126,13 +126,14 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
   // (`slot_a` belongs to the item that the next produce() call will request, `slot_b` to the one
   // after), so that the producer never waits for that load.  The load is a volatile asm
   // statement: the compiler would otherwise move it down to its use.
-  // kShift: lanes 16 and 17 fetch the first and the last slot of the tile in front as well.
+  // kShift: lanes 16, 17 and 18 fetch the first, last and ninth slot of the tile in front as well.
   auto load_slot = [&](unsigned item) -> int64_t {
     if (item >= items) return -1;
     const int tile = int((item >= pairs ? item - pairs : item) / HH);
     int tok = tile * kStagedTile + (lane & 15);
     if constexpr (kShift) {
-      if (lane >= 16) tok = lane < 18 ? (tile - 1) * kStagedTile + (lane & 1) * (kStagedTile - 1) : -1;
+      if (lane >= 16)
+        tok = lane < 19 ? (tile - 1) * kStagedTile + (lane == 16 ? 0 : (lane == 17 ? kStagedTile - 1 : 8)) : -1;
     }
     if (tok < 0 || tok >= p.num_tokens) return -1;
     int64_t v;
@@ -146,7 +147,8 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
   // sequence, whatever blocks they are in) therefore covers the 16 tokens from the next 16-slot
   // boundary on: tokens [16 i + shift, 16 i + shift + 16), 0 <= shift < 16.  The tokens
   // [16 i, 16 i + shift) that it gives up lie in the window of tile i - 1 if that one is shifted
-  // by at least as much - every tile can tell, the shift is a function of a tile's own slots;
+  // by at least as much - every tile can tell, the shift is a function of a tile's own slots
+  // (three of them, and the same function for a tile and for its successor looking back at it);
   // otherwise tile i writes them itself from global memory (`head` in the consumer; once per
   // run).  Windows may overlap: a slot is then written twice with the same bytes.  The rule is
   // only a guess about the slots; whatever they are, every token is written, with its own slot.
@@ -166,10 +168,11 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
       const int64_t f = __shfl_sync(0xffffffffu, cand, 0), m = __shfl_sync(0xffffffffu, cand, 8);
       const int64_t l = __shfl_sync(0xffffffffu, cand, 15);
       const int64_t pf = __shfl_sync(0xffffffffu, cand, 16), pl = __shfl_sync(0xffffffffu, cand, 17);
+      const int64_t pm = __shfl_sync(0xffffffffu, cand, 18);
       const int d = shift_of(f, m, l);
       if (d == 0) return cand;  // (the shift of the tile in front does not matter then)
-      // the tile in front: its ninth slot is not at hand; first and last decide
-      const int dp = (pf >= 0 && pl >= 0 && ((pl - pf) & 15) == 15) ? int((kStagedTile - (pf & 15)) & 15) : 0;
+      // the tile in front, by the very rule that its own warp applies
+      const int dp = shift_of(pf, pm, pl);
       sh = d | (dp << 8);
       const int tile = int((item >= pairs ? item - pairs : item) / HH);
       const int tok = tile * kStagedTile + d + (lane & 15);
