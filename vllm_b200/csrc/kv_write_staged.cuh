@@ -100,6 +100,11 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
   // evenly over warps and SMs.
   const unsigned HH = unsigned(H) * unsigned(HS);  // (head, piece of the head) pairs per tile
   const unsigned pairs = unsigned(tiles) * HH;
+  // pair number / HH by one multiply-high (exact while pairs * HH < 2^32): the item bookkeeping
+  // would otherwise spend four runtime divisions per item
+  const uint32_t hh_m = HH > 1 ? 0xFFFFFFFFu / HH + 1 : 0;  // ceil(2^32 / HH)
+  const bool hh_fast = uint64_t(pairs) * HH <= 0xFFFFFFFFull;
+  auto div_hh = [&](unsigned n) -> unsigned { return HH == 1 ? n : (hh_fast ? __umulhi(n, hh_m) : n / HH); };
   const unsigned items = pairs * 2u;
   const unsigned grid_warps = gridDim.x * unsigned(nwarps);
   unsigned next_item = unsigned(warp) * gridDim.x + blockIdx.x;
@@ -129,7 +134,7 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
   // kShift: lanes 16, 17 and 18 fetch the first, last and ninth slot of the tile in front as well.
   auto load_slot = [&](unsigned item) -> int64_t {
     if (item >= items) return -1;
-    const int tile = int((item >= pairs ? item - pairs : item) / HH);
+    const int tile = int(div_hh(item >= pairs ? item - pairs : item));
     int tok = tile * kStagedTile + (lane & 15);
     if constexpr (kShift) {
       if (lane >= 16)
@@ -174,7 +179,7 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
       // the tile in front, by the very rule that its own warp applies
       const int dp = shift_of(pf, pm, pl);
       sh = d | (dp << 8);
-      const int tile = int((item >= pairs ? item - pairs : item) / HH);
+      const int tile = int(div_hh(item >= pairs ? item - pairs : item));
       const int tok = tile * kStagedTile + d + (lane & 15);
       if (tok >= p.num_tokens) return -1;
       int64_t v;
@@ -192,7 +197,7 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
   auto produce = [&](unsigned item, int stage) {
     const bool is_v = item >= pairs;
     const unsigned pr = is_v ? item - pairs : item;
-    const int tile = int(pr / HH);
+    const int tile = int(div_hh(pr));
     const int hp = int(pr - unsigned(tile) * HH);  // head * HS + piece
     const int t = lane & 15;
     const int sh = sh_a;
@@ -249,8 +254,9 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
     const unsigned char* st = my_stages + size_t(cons_stage) * p.stage_bytes;
     const bool is_v = cur_item >= pairs;
     const unsigned cur_pr = is_v ? cur_item - pairs : cur_item;
-    const int hp = int(cur_pr % HH);
-    const int h = hp / HS;
+    const int cur_tile = int(div_hh(cur_pr));
+    const int hp = int(cur_pr - unsigned(cur_tile) * HH);
+    const int h = HS == 2 ? hp >> 1 : hp;
     const int piece = hp - h * HS;
     // lane t (and t + 16) knows token t's cache block and offset
     const int64_t slot = reinterpret_cast<const int64_t*>(st + slot_off)[lane & 15];
@@ -264,7 +270,7 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
       // ---- tokens in front of a moved window that no other window covers (see above): at most
       // 15, straight from global memory, all loads independent of each other
       const int sh = *reinterpret_cast<const int*>(st + sh_off);
-      const int tile = int(cur_pr / HH);
+      const int tile = cur_tile;
       const int hb = tile * kStagedTile + (tile > 0 ? ((sh >> 8) & 0xff) : 0);
       const int nh = min(tile * kStagedTile + (sh & 0xff), p.num_tokens) - hb;
       if (nh > 0) {
