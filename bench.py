@@ -520,6 +520,8 @@ def main() -> int:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--headline-only", action="store_true",
                     help="skip the other configurations and the strong-scaling section")
+    ap.add_argument("--shard-of", type=int, default=0,
+                    help="cfg4 / cfg5: time rank 0's shard of an N-way sharded run on this GPU (for profiles)")
     ap.add_argument("--num-seqs", type=int, default=None,
                     help="override the batch size of cfg2/cfg3/cfg5 (small cases for profiler captures)")
     a = ap.parse_args()
@@ -538,7 +540,10 @@ def main() -> int:
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
 
-    w, version, scaling = build_workload(a.workload, dev, world, rank, a.num_seqs)
+    if a.shard_of > 1 and world == 1:
+        w, version, scaling = build_workload(a.workload, dev, a.shard_of, 0, a.num_seqs)
+    else:
+        w, version, scaling = build_workload(a.workload, dev, world, rank, a.num_seqs)
     cfg = {
         "workload": f"{w.name}: paged_attention_{version}, num_seqs={w.num_seqs} per GPU, "
                     f"{w.num_heads} query / {w.num_kv_heads} KV heads, head_size={w.head_size}, "
