@@ -3,6 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
                     [--workload cfg2|cfg1|cfg3|cfg4|cfg5|cfg3w|cfg3wf] [--headline-only]
+                    [--shard-of N] [--num-seqs S]
 
 One "step" is one decode call (one new token per sequence, one layer) of
 ``paged_attention_v2`` over the whole synthetic batch.  The default workload is
