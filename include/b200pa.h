@@ -290,10 +290,13 @@ int b200pa_version(void);
 
 /*
  * Reads (and clears) the device-side status word of the current device.  The
- * decode kernel's mbarrier waits are bounded; a wait that runs out records a
- * code here and the kernel returns instead of spinning.  This call synchronises
- * the device; it is meant for tests and debugging, never for the hot path.
- * Returns 0 and stores the word (0 = healthy) in *status.
+ * kernels' mbarrier waits are bounded; a wait that runs out records a code here
+ * and the warp returns instead of spinning.  Codes: 0 healthy, 1 a wait ran out,
+ * 2 a warp was handed work without shared-memory ring slots, 3 a warp owed more
+ * split-KV merges than it can note down (2 and 3 guard invariants of the work
+ * distribution and are not expected to occur).  This call synchronises the
+ * device; it is meant for tests and debugging, never for the hot path.
+ * Returns 0 and stores the word in *status.
  */
 int b200pa_device_status(int32_t* status);
 
