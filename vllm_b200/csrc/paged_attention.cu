@@ -643,7 +643,8 @@ static int attention_entry(const b200pa_attn_args* a, void* stream, Scratch mode
     const size_t table_bytes = split ? table_full : 0;
     const size_t budget = ring_budget(split);
     int nwarps = warps_for(budget);
-    if (tune.warps) nwarps = std::max(1, std::min(ki.max_warps, tune.warps));
+    if (tune.warps)  // (never more than the shared memory has ring slots for)
+      nwarps = std::max(1, std::min({ki.max_warps, tune.warps, int(budget / (min_slots * slot_bytes))}));
     // Ring slots per warp: two.  Measured on B200, a launch with work for every warp is 3-5 %
     // slower when the CTA is given shared memory for four slots per warp, even if only two of
     // them are kept in flight; a split launch whose batch turns out to have fewer ranges than
