@@ -10,15 +10,16 @@
 //   * a work item is 16 consecutive tokens of one head of K, or of V: its 16 rows (head_size
 //     elements each) are fetched with one bulk async copy per row, issued by 16 lanes at once,
 //     up to `stages - 1` items ahead of the one being converted;
-//   * rows land at a pitch of row bytes + 16, which makes the two access patterns below free of
-//     bank conflicts;
+//   * rows land at a pitch of row bytes + 16 in a permuted order of row slots, which makes the
+//     two access patterns below free of bank conflicts;
 //   * K (both layouts) and V of the flash layout: a lane converts 16 bytes of output of one
 //     token - lanes run over tokens first, so a warp's stores fill whole 256-byte runs of a
 //     cache page whenever the tokens sit in consecutive slots;
-//   * V of the x-layout is a transpose ([token][d] -> [d][token in block]): a lane reads two
-//     adjacent d of all 16 tokens from shared memory, converts the two rows and writes each
-//     with one 16-byte store when the tile fills 16 aligned consecutive slots, else four bytes
-//     at a time where consecutive tokens allow it, else element by element (decode steps);
+//   * V of the x-layout is a transpose ([token][d] -> [d][token in block]), done by
+//     ldmatrix.trans: a lane receives four consecutive tokens of one d as two words, converts
+//     them and stores four bytes (eight for a 16-bit cache) when the tokens sit in four aligned
+//     consecutive slots - 128-byte (256-byte) runs per warp store when the whole tile does -
+//     else element by element (decode steps);
 //   * small writes cut a head of 128 into two work items (hsplit), which halves the latency of
 //     the one item a warp then has;
 //   * the kShift instantiation (large x-layout writes) moves a tile whose tokens are consecutive
@@ -57,6 +58,8 @@ struct StagedWriteParams {
 };
 
 constexpr int kStagedTile = 16;  // tokens per work item
+// Row slot of token t in a stage (tokens 8..15 swap places in pairs of two: see the V path).
+__device__ __forceinline__ int staged_row(int t) { return t ^ ((t >> 2) & 2); }
 constexpr int kStagedMaxWarps = 24;
 
 // 16 input elements (two 16-byte shared-memory reads) -> 16 bytes of cache, or 8 -> 16 for a
@@ -124,7 +127,7 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
   const char* val_b = static_cast<const char*>(p.value);
   const uint64_t policy = policy_evict_first();
 
-  // a stage: 16 rows, then the 16 slots of the tile
+  // a stage: the 16 rows (token t in row slot staged_row(t)), then the 16 slots of the tile
   const int slot_off = kStagedTile * p.pitch;
 
   // The slot of a token is needed before its row can be requested; it is loaded two items ahead
@@ -220,7 +223,7 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
     if (valid) {
       const char* src = (is_v ? val_b : key_b) +
                         (int64_t(tok) * (is_v ? p.value_stride : p.key_stride) + int64_t(hp) * DP) * 2;
-      bulk_g2s(smem_u32(st) + t * p.pitch, src, uint32_t(row_bytes), bar, policy);
+      bulk_g2s(smem_u32(st) + staged_row(t) * p.pitch, src, uint32_t(row_bytes), bar, policy);
     }
   };
 
@@ -330,7 +333,7 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
       const int c_first = piece * my_chunks;
       const int t = lane & 15;
       const ScaledDiv& div = is_v ? v_div : k_div;
-      const unsigned char* rows = st + t * p.pitch;
+      const unsigned char* rows = st + staged_row(t) * p.pitch;
       unsigned char* dst;
       int64_t cstep;  // bytes between two chunks of one token in the cache
       if constexpr (kFlash) {
@@ -349,100 +352,79 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
         }
       }
     } else {
-      // ================= V of the x-layout: transpose, two adjacent d per lane
-      const int64_t s0 = __shfl_sync(0xffffffffu, slot, 0);
-      const bool in_run = (lane >= kStagedTile) || slot == s0 + lane;
-      const bool full_run = __all_sync(0xffffffffu, in_run) && vmask == 0xffffu && s0 % kStagedTile == 0 &&
-                            B % kStagedTile == 0;
-      constexpr int W4 = 4 / E;  // tokens per 4-byte store
-      // tokens that start a 4-byte group: aligned slot, the next W4 - 1 tokens follow in the block
-      bool follows = valid;
+      // ================= V of the x-layout: a transpose ([token][d] -> [d][token in block]), done
+      // by ldmatrix.trans.  One instruction hands every lane, for row d = lane / 4 of an 8-d
+      // group, two 32-bit words of two tokens each; the token rows that form its 8x8 matrices
+      // are chosen so that lane j = lane % 4 receives tokens 4 j .. 4 j + 3 (matrix A = tokens
+      // 0 1 4 5 8 9 12 13, matrix B = the others), i.e. four consecutive bytes (fp8) or eight
+      // (16-bit cache) of the cache row, in the word format that the quantiser takes.  The row
+      // slots (staged_row) make the eight rows of either matrix, and the eight tokens of either
+      // half of the tile that the K path reads together, fall into different bank groups.  A lane stores its four tokens with one word store when they sit in four
+      // consecutive, aligned slots of one block, else one by one; eight lanes-of-four make a
+      // 128-byte (256-byte) run of the cache when the whole tile is such a run.
+      const int j = lane & 3;
+      // this lane's four tokens: slots, validity, where they go (element index of row d = 0)
+      int64_t tb[4];
+      bool tv[4];
 #pragma unroll
-      for (int k = 1; k < W4; ++k) {
-        const int64_t sk = __shfl_down_sync(0xffffffffu, slot, k);
-        follows &= ((lane & 15) + k < kStagedTile) && sk == slot + k;
+      for (int k = 0; k < 4; ++k) {
+        const int64_t sk = reinterpret_cast<const int64_t*>(st + slot_off)[4 * j + k];
+        tv[k] = sk >= 0;
+        const int64_t bk = !tv[k] ? 0 : (b_shift >= 0 ? sk >> b_shift : sk / B);
+        tb[k] = ((bk * H + h) * int64_t(D) + piece * DP) * B + (tv[k] ? sk - bk * B : 0);
       }
-      const unsigned starts =
-          __ballot_sync(0xffffffffu, follows && (off * E) % 4 == 0 && off + W4 <= B && (B * E) % 4 == 0) & 0xffffu;
-      unsigned char* vbase = static_cast<unsigned char*>(p.value_cache);
-      const unsigned char* vrows = st;
-      // every lane runs every iteration (the stores below use warp shuffles); lanes whose pair
-      // of rows lies beyond the head size only take part in those
-      const int d_first = piece * DP;
-      for (int d_base = 0; d_base < DP; d_base += 64) {
-        const int dl = d_base + 2 * lane;  // inside the item
-        const int d0 = d_first + dl;       // inside the head
-        const bool mine = dl < DP;
-        uint32_t two[kStagedTile];  // token t: (d0, d0 + 1)
-        if (mine) {
-          const unsigned char* col = vrows + dl * 2;
-          const int pitch = p.pitch;
+      const int64_t s0 = reinterpret_cast<const int64_t*>(st + slot_off)[4 * j];
+      bool quad = tv[0] && tv[1] && tv[2] && tv[3];
 #pragma unroll
-          for (int t = 0; t < kStagedTile; ++t) two[t] = *reinterpret_cast<const uint32_t*>(col + t * pitch);
-        } else {
-#pragma unroll
-          for (int t = 0; t < kStagedTile; ++t) two[t] = 0u;
-        }
-        if (vmask != 0xffffu) {  // stale shared memory in the rows of skipped tokens
-#pragma unroll
-          for (int t = 0; t < kStagedTile; ++t)
-            if (!((vmask >> t) & 1u)) two[t] = 0u;
-        }
-        __align__(16) cache_t c0[kStagedTile], c1[kStagedTile];
+      for (int k = 1; k < 4; ++k) quad = quad && reinterpret_cast<const int64_t*>(st + slot_off)[4 * j + k] == s0 + k;
+      quad = quad && (s0 & 3) == 0 && B % 4 == 0;
+      // ldmatrix row address of this lane: matrix lane / 8 = (token set) + 2 * (d half), row lane % 8
+      const int mr = lane & 7, mi = lane >> 3;
+      const int mtok = (mr >> 1) * 4 + (mr & 1) + (mi & 1) * 2;
+      const uint32_t maddr = smem_u32(st) + uint32_t(staged_row(mtok) * p.pitch + (mi >> 1) * 16);
+      cache_t* vbase = static_cast<cache_t*>(p.value_cache);
+      for (int d16 = 0; d16 < DP; d16 += 16) {
+        uint32_t r0, r1, r2, r3;  // (tokens 4j, 4j+1), (4j+2, 4j+3) of row d; the same of row d + 8
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                     : "r"(maddr + uint32_t(d16) * 2u));
+        const int d = d16 + (lane >> 2);
+        uint32_t lo[2], hi[2];  // this lane's piece of row d and of row d + 8 (one word when fp8)
         if constexpr (KV != kKvAuto) {
-          // row d0 takes the low halves of consecutive tokens' words, row d0 + 1 the high halves
-          uint32_t w0[kStagedTile / 2], w1[kStagedTile / 2], o0[kStagedTile / 4], o1[kStagedTile / 4];
-#pragma unroll
-          for (int t = 0; t < kStagedTile; t += 2) {
-            w0[t / 2] = __byte_perm(two[t], two[t + 1], 0x5410u);
-            w1[t / 2] = __byte_perm(two[t], two[t + 1], 0x7632u);
-          }
-          convert_words<in_t, KV, kStagedTile / 2>(w0, o0, v_div);
-          convert_words<in_t, KV, kStagedTile / 2>(w1, o1, v_div);
-#pragma unroll
-          for (int i = 0; i < kStagedTile / 4; ++i) {
-            reinterpret_cast<uint32_t*>(c0)[i] = o0[i];
-            reinterpret_cast<uint32_t*>(c1)[i] = o1[i];
-          }
+          const uint32_t wa[2] = {r0, r1}, wb[2] = {r2, r3};
+          uint32_t oa[1], ob[1];
+          convert_words<in_t, KV, 2>(wa, oa, v_div);
+          convert_words<in_t, KV, 2>(wb, ob, v_div);
+          lo[0] = oa[0];
+          hi[0] = ob[0];
+          lo[1] = hi[1] = 0;
         } else {
-#pragma unroll
-          for (int t = 0; t < kStagedTile; t += 2) {
-            reinterpret_cast<uint32_t*>(c0)[t / 2] = __byte_perm(two[t], two[t + 1], 0x5410u);
-            reinterpret_cast<uint32_t*>(c1)[t / 2] = __byte_perm(two[t], two[t + 1], 0x7632u);
-          }
+          lo[0] = r0;
+          lo[1] = r1;
+          hi[0] = r2;
+          hi[1] = r3;
         }
-        if (full_run) {
-          const int64_t b0 = b_shift >= 0 ? s0 >> b_shift : s0 / B;
-          unsigned char* dst = vbase + (((b0 * H + h) * int64_t(D) + d0) * B + int(s0 - b0 * B)) * E;
-          if (mine) {
-#pragma unroll
-            for (int w = 0; w < kStagedTile * E / 16; ++w) {
-              reinterpret_cast<uint4*>(dst)[w] = reinterpret_cast<const uint4*>(c0)[w];
-              reinterpret_cast<uint4*>(dst + int64_t(B) * E)[w] = reinterpret_cast<const uint4*>(c1)[w];
-            }
+        const int64_t rowoff = int64_t(d) * B;  // row d; row d + 8 lies 8 * B elements further
+        if (quad) {
+          cache_t* dst = vbase + tb[0] + rowoff;
+          if constexpr (E == 1) {
+            *reinterpret_cast<uint32_t*>(dst) = lo[0];
+            *reinterpret_cast<uint32_t*>(dst + 8 * int64_t(B)) = hi[0];
+          } else {
+            *reinterpret_cast<uint2*>(dst) = make_uint2(lo[0], lo[1]);
+            *reinterpret_cast<uint2*>(dst + 8 * int64_t(B)) = make_uint2(hi[0], hi[1]);
           }
         } else {
-          unsigned covered = 0;  // tokens written as part of an earlier group
 #pragma unroll
-          for (int t = 0; t < kStagedTile; ++t) {
-            if (!((vmask >> t) & 1u) || ((covered >> t) & 1u)) continue;  // warp-uniform
-            const int64_t bt = __shfl_sync(0xffffffffu, blk, t);
-            const int ot = __shfl_sync(0xffffffffu, off, t);
-            unsigned char* dst = vbase + (((bt * H + h) * int64_t(D) + d0) * B + ot) * E;
-            if (!mine) continue;
-            if (W4 > 1 && ((starts >> t) & 1u) && t + W4 <= kStagedTile) {
-              __align__(4) cache_t g0[W4], g1[W4];
-#pragma unroll
-              for (int k = 0; k < W4; ++k) {
-                g0[k] = c0[(t + k) % kStagedTile];
-                g1[k] = c1[(t + k) % kStagedTile];
-              }
-              *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(g0);
-              *reinterpret_cast<uint32_t*>(dst + int64_t(B) * E) = *reinterpret_cast<const uint32_t*>(g1);
-              covered |= ((1u << W4) - 1u) << t;
+          for (int k = 0; k < 4; ++k) {
+            if (!tv[k]) continue;
+            cache_t* dst = vbase + tb[k] + rowoff;
+            if constexpr (E == 1) {
+              *reinterpret_cast<unsigned char*>(dst) = static_cast<unsigned char>(lo[0] >> (8 * k));
+              *reinterpret_cast<unsigned char*>(dst + 8 * int64_t(B)) = static_cast<unsigned char>(hi[0] >> (8 * k));
             } else {
-              *reinterpret_cast<cache_t*>(dst) = c0[t];
-              *reinterpret_cast<cache_t*>(dst + int64_t(B) * E) = c1[t];
+              *reinterpret_cast<uint16_t*>(dst) = static_cast<uint16_t>(lo[k >> 1] >> (16 * (k & 1)));
+              *reinterpret_cast<uint16_t*>(dst + 8 * int64_t(B)) = static_cast<uint16_t>(hi[k >> 1] >> (16 * (k & 1)));
             }
           }
         }
