@@ -383,51 +383,76 @@ __global__ void __launch_bounds__(kStagedMaxWarps * 32, 1) kv_write_staged_kerne
       const int mtok = (mr >> 1) * 4 + (mr & 1) + (mi & 1) * 2;
       const uint32_t maddr = smem_u32(st) + uint32_t(staged_row(mtok) * p.pitch + (mi >> 1) * 16);
       cache_t* vbase = static_cast<cache_t*>(p.value_cache);
-      for (int d16 = 0; d16 < DP; d16 += 16) {
-        uint32_t r0, r1, r2, r3;  // (tokens 4j, 4j+1), (4j+2, 4j+3) of row d; the same of row d + 8
-        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                     : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-                     : "r"(maddr + uint32_t(d16) * 2u));
-        const int d = d16 + (lane >> 2);
-        uint32_t lo[2], hi[2];  // this lane's piece of row d and of row d + 8 (one word when fp8)
-        if constexpr (KV != kKvAuto) {
-          const uint32_t wa[2] = {r0, r1}, wb[2] = {r2, r3};
-          uint32_t oa[1], ob[1];
-          convert_words<in_t, KV, 2>(wa, oa, v_div);
-          convert_words<in_t, KV, 2>(wb, ob, v_div);
-          lo[0] = oa[0];
-          hi[0] = ob[0];
-          lo[1] = hi[1] = 0;
-        } else {
-          lo[0] = r0;
-          lo[1] = r1;
-          hi[0] = r2;
-          hi[1] = r3;
-        }
-        const int64_t rowoff = int64_t(d) * B;  // row d; row d + 8 lies 8 * B elements further
-        if (quad) {
-          cache_t* dst = vbase + tb[0] + rowoff;
-          if constexpr (E == 1) {
-            *reinterpret_cast<uint32_t*>(dst) = lo[0];
-            *reinterpret_cast<uint32_t*>(dst + 8 * int64_t(B)) = hi[0];
-          } else {
-            *reinterpret_cast<uint2*>(dst) = make_uint2(lo[0], lo[1]);
-            *reinterpret_cast<uint2*>(dst + 8 * int64_t(B)) = make_uint2(hi[0], hi[1]);
-          }
-        } else {
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            if (!tv[k]) continue;
-            cache_t* dst = vbase + tb[k] + rowoff;
-            if constexpr (E == 1) {
-              *reinterpret_cast<unsigned char*>(dst) = static_cast<unsigned char>(lo[0] >> (8 * k));
-              *reinterpret_cast<unsigned char*>(dst + 8 * int64_t(B)) = static_cast<unsigned char>(hi[0] >> (8 * k));
+      // One pass over the item's rows.  fp8: the fast pass quantises without looking at the
+      // codes and only collects whether any of them is a NaN code (a NaN, or a quotient that
+      // overflowed on the way); if so - rare - the item is done again with the division, which
+      // overwrites what the fast pass stored.
+      auto pass = [&](auto exact_tag) -> uint32_t {
+        constexpr bool kExact = decltype(exact_tag)::value;
+        (void)kExact;
+        uint32_t nan_bits = 0;
+        for (int d16 = 0; d16 < DP; d16 += 16) {
+          uint32_t r0, r1, r2, r3;  // (tokens 4j, 4j+1), (4j+2, 4j+3) of row d; the same of row d + 8
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                       : "r"(maddr + uint32_t(d16) * 2u));
+          const int d = d16 + (lane >> 2);
+          uint32_t lo[2], hi[2];  // this lane's piece of row d and of row d + 8 (one word when fp8)
+          if constexpr (KV != kKvAuto) {
+            if constexpr (kExact) {
+              const uint32_t wa[2] = {r0, r1}, wb[2] = {r2, r3};
+              uint32_t oa[1], ob[1];
+              convert_words<in_t, KV, 2>(wa, oa, v_div);  // (checks its own codes)
+              convert_words<in_t, KV, 2>(wb, ob, v_div);
+              lo[0] = oa[0];
+              hi[0] = ob[0];
             } else {
-              *reinterpret_cast<uint16_t*>(dst) = static_cast<uint16_t>(lo[k >> 1] >> (16 * (k & 1)));
-              *reinterpret_cast<uint16_t*>(dst + 8 * int64_t(B)) = static_cast<uint16_t>(hi[k >> 1] >> (16 * (k & 1)));
+              const uint32_t va = neg_quant4<in_t, KV == kKvE5M2>(r0, r1, v_div);
+              const uint32_t vb = neg_quant4<in_t, KV == kKvE5M2>(r2, r3, v_div);
+              nan_bits |= ((va & 0x7F7F7F7Fu) + 0x01010101u) | ((vb & 0x7F7F7F7Fu) + 0x01010101u);
+              lo[0] = va ^ 0x80808080u;
+              hi[0] = vb ^ 0x80808080u;
+            }
+            lo[1] = hi[1] = 0;
+          } else {
+            lo[0] = r0;
+            lo[1] = r1;
+            hi[0] = r2;
+            hi[1] = r3;
+          }
+          const int64_t rowoff = int64_t(d) * B;  // row d; row d + 8 lies 8 * B elements further
+          if (quad) {
+            cache_t* dst = vbase + tb[0] + rowoff;
+            if constexpr (E == 1) {
+              *reinterpret_cast<uint32_t*>(dst) = lo[0];
+              *reinterpret_cast<uint32_t*>(dst + 8 * int64_t(B)) = hi[0];
+            } else {
+              *reinterpret_cast<uint2*>(dst) = make_uint2(lo[0], lo[1]);
+              *reinterpret_cast<uint2*>(dst + 8 * int64_t(B)) = make_uint2(hi[0], hi[1]);
+            }
+          } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              if (!tv[k]) continue;
+              cache_t* dst = vbase + tb[k] + rowoff;
+              if constexpr (E == 1) {
+                *reinterpret_cast<unsigned char*>(dst) = static_cast<unsigned char>(lo[0] >> (8 * k));
+                *reinterpret_cast<unsigned char*>(dst + 8 * int64_t(B)) = static_cast<unsigned char>(hi[0] >> (8 * k));
+              } else {
+                *reinterpret_cast<uint16_t*>(dst) = static_cast<uint16_t>(lo[k >> 1] >> (16 * (k & 1)));
+                *reinterpret_cast<uint16_t*>(dst + 8 * int64_t(B)) = static_cast<uint16_t>(hi[k >> 1] >> (16 * (k & 1)));
+              }
             }
           }
         }
+        return nan_bits & 0x80808080u;
+      };
+      if constexpr (KV == kKvAuto) {
+        pass(std::false_type{});
+      } else {
+        // (ldmatrix is warp-collective: the decision to repeat is taken by the warp)
+        const bool again = !v_div.fast || __any_sync(0xffffffffu, pass(std::false_type{}) != 0);
+        if (again) pass(std::true_type{});
       }
     }
 
