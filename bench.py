@@ -80,37 +80,18 @@ def ncu_traffic_ratio(name: str):
 
 
 class ClockSampler:
-    """Samples the SM clock and the throttle reasons of one GPU while the timed region runs:
-    through NVML every millisecond or so (the timed region of the default run lasts a few
-    milliseconds), else through `nvidia-smi -lms 100`.  Read-only."""
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
 
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
-    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, index: int):
         self.index = index
-        self.rows = []      # nvidia-smi lines
-        self.sm = []        # NVML samples
-        self.reason_bits = 0
+        self.rows = []
         self.proc = None
-        self.nvml = None
-        self.stop_flag = False
 
     def start(self):
-        try:
-            import pynvml
-
-            pynvml.nvmlInit()
-            self.nvml = pynvml
-            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
-            self.max_sm = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
-            self.t = threading.Thread(target=self._poll, daemon=True)
-            self.t.start()
-            return
-        except Exception:
-            self.nvml = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
@@ -121,34 +102,11 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
-    def _poll(self):
-        n = self.nvml
-        while not self.stop_flag:
-            try:
-                self.sm.append(float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)))
-                self.reason_bits |= int(n.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
-            except Exception:
-                break
-            time.sleep(0.001)
-
     def _read(self):
         for line in self.proc.stdout:
             self.rows.append(line.strip())
 
     def stop(self):
-        if self.nvml is not None:
-            self.stop_flag = True
-            self.t.join(timeout=2)
-            n = self.nvml
-            bits = {
-                "hw_slowdown": getattr(n, "nvmlClocksEventReasonHwSlowdown", 0x8),
-                "hw_thermal_slowdown": getattr(n, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
-                "sw_thermal_slowdown": getattr(n, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
-                "sw_power_cap": getattr(n, "nvmlClocksEventReasonSwPowerCap", 0x4),
-            }
-            reasons = sorted(k for k, v in bits.items() if self.reason_bits & v)
-            return {"sm_mhz": float(np.median(self.sm)) if self.sm else None, "sm_max_mhz": self.max_sm,
-                    "samples": len(self.sm), "reasons": reasons, "source": "nvml"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -158,6 +116,7 @@ class ClockSampler:
         except Exception:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for r in self.rows:
             parts = [p.strip() for p in r.split(",")]
             if len(parts) < 6:
@@ -167,12 +126,12 @@ class ClockSampler:
                 mx.append(float(parts[1]))
             except ValueError:
                 continue
-            for n, v in zip(self.NAMES, parts[2:6]):
+            for n, v in zip(names, parts[2:6]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": float(np.median(sm)) if sm else None,
                 "sm_max_mhz": float(max(mx)) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons), "source": "nvidia-smi"}
+                "samples": len(sm), "reasons": sorted(reasons)}
 
 
 class L2Flush:
@@ -647,7 +606,6 @@ def main() -> int:
         e.record()
     barrier()
     t_wall = time.perf_counter() - t_wall
-    clocks = sampler.stop()  # (samples of the timed region only)
     launches = capi.launch_count()
     per_step = [s.elapsed_time(e) for s, e in evs]
     ms = float(np.mean(per_step))
@@ -744,6 +702,7 @@ def main() -> int:
             ms_e2e = e0.elapsed_time(e1) / a.steps
             assert torch.equal(houts[(a.steps - 1) & 1], out.cpu()), "e2e output differs from the resident run"
         w.query, w.block_tables, w.seq_lens = wq, wbt, wsl
+    clocks = sampler.stop()
 
     # ---- max over ranks, whole-job aggregate
     seqs_total = units_rank
