@@ -162,3 +162,55 @@ def test_reference_names_are_claimed_on_request_and_never_twice():
                        cwd=str(__import__("pathlib").Path(__file__).resolve().parents[1]))
     assert r.returncode == 0, r.stderr[-2000:]
     assert r.stdout.split() == ["False", "8", "True", "0"]
+
+
+def test_moved_tiles_of_the_kv_write_cover_every_token():
+    """The staged KV write may move a 16-token tile onto the next 16-slot boundary of the cache
+    (vllm_b200/csrc/kv_write_staged.cuh, `shift_of`): tile i then covers tokens
+    [16 i + s_i, 16 i + s_i + 16) and writes the tokens [16 i + s_(i-1), 16 i + s_i) in front of
+    its window itself when the tile before it is moved by less.  Whatever the slots are, every
+    token must be covered at least once.  This restates the rule on the host and checks the
+    property on random slot mappings (runs of consecutive slots at odd offsets, scattered tokens,
+    padding)."""
+    import numpy as np
+
+    def shift_of(first, mid, last):
+        if first < 0 or mid < 0 or last < 0:
+            return 0
+        if (mid - first) % 16 != 8 or (last - first) % 16 != 15:
+            return 0
+        return (16 - first % 16) % 16
+
+    def tile_shift(slots, i):
+        T = len(slots)
+        tok = [16 * i, 16 * i + 8, 16 * i + 15]
+        if i < 0 or tok[2] >= T:
+            return 0
+        return shift_of(*(int(slots[t]) for t in tok))
+
+    rng = np.random.default_rng(5)
+    for _ in range(300):
+        pieces, free = [], 0
+        for _ in range(int(rng.integers(1, 30))):
+            kind = int(rng.integers(4))
+            if kind == 0:
+                free += int(rng.integers(1, 80))
+                pieces.append(np.array([free]))
+                free += 1
+            elif kind == 1:
+                pieces.append(np.full(int(rng.integers(1, 9)), -1))
+            else:
+                n = int(rng.integers(1, 90))
+                free += int(rng.integers(0, 48))
+                pieces.append(np.arange(free, free + n))
+                free += n
+        order = rng.permutation(len(pieces))
+        slots = np.concatenate([pieces[k] for k in order])
+        T = len(slots)
+        covered = np.zeros(T, dtype=int)
+        for i in range((T + 15) // 16):
+            s, sp = tile_shift(slots, i), tile_shift(slots, i - 1)
+            covered[16 * i + s:min(16 * i + s + 16, T)] += 1          # the window
+            if s > 0:
+                covered[16 * i + (sp if i > 0 else 0):min(16 * i + s, T)] += 1  # the tokens in front
+        assert (covered >= 1).all(), (slots.tolist(), covered.tolist())
